@@ -1,0 +1,72 @@
+// Shared helpers of the sm_100a kernel library. Every exported function is
+// extern "C", takes raw device pointers and a CUDA stream, launches on that
+// stream and returns a cudaError_t as int (0 = launched). Arguments are
+// validated on the host before a launch: a size the kernel cannot take is
+// refused with LUMEN_ERR_UNSUPPORTED, never computed wrongly.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <stdint.h>
+
+#define LUMEN_API extern "C" __attribute__((visibility("default")))
+
+// Error codes above the CUDA range, understood by the Python loader.
+#define LUMEN_ERR_UNSUPPORTED 100001
+#define LUMEN_ERR_BAD_ARGUMENT 100002
+
+// Tokens per page of the paged key/value cache. A page holds, for one cache
+// entry (one run of a layer), [n_kv][LUMEN_PAGE][head_dim] keys (and the same
+// for values), so one (page, kv head) tile is contiguous.
+#define LUMEN_PAGE 64
+
+#define LUMEN_LAUNCH_CHECK()                         \
+    do {                                             \
+        cudaError_t e__ = cudaGetLastError();        \
+        if (e__ != cudaSuccess) return (int)e__;     \
+    } while (0)
+
+__device__ __forceinline__ float to_f32(float x) { return x; }
+__device__ __forceinline__ float to_f32(__nv_bfloat16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_f32(float x);
+template <> __device__ __forceinline__ float from_f32<float>(float x) { return x; }
+template <> __device__ __forceinline__ __nv_bfloat16 from_f32<__nv_bfloat16>(float x) {
+    return __float2bfloat16_rn(x);
+}
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Block-wide sum with a fixed order (warp butterflies, then warp 0 over the
+// per-warp partials), so the result depends only on the block size.
+// `red` must hold 32 floats. All threads get the result.
+__device__ __forceinline__ float block_sum(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_sum(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarp) ? red[lane] : 0.0f;
+    t = warp_sum(t);
+    return t;
+}
+__device__ __forceinline__ float block_max(float v, float* red) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    const int nwarp = (blockDim.x + 31) >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) red[warp] = v;
+    __syncthreads();
+    float t = (lane < nwarp) ? red[lane] : -INFINITY;
+    t = warp_max(t);
+    return t;
+}

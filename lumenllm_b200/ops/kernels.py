@@ -1,0 +1,182 @@
+"""Python faces of the hand-written kernels. Each function checks dtypes and
+shapes, launches on the current CUDA stream and returns its output tensor.
+Float32 tensors select the 32-bit variants, bfloat16 tensors the serving ones.
+"""
+from __future__ import annotations
+
+from ctypes import c_float, c_int, c_longlong, c_void_p
+
+import torch
+
+from .native import KernelError, check, fn, ptr, require, stream_ptr
+
+P = c_void_p
+F32 = torch.float32
+BF16 = torch.bfloat16
+I32 = torch.int32
+
+PAGE = 64  # tokens per cache page; equals LUMEN_PAGE in csrc/common.cuh
+
+
+def _is_bf16(t) -> int:
+    if t.dtype == BF16:
+        return 1
+    if t.dtype == F32:
+        return 0
+    raise KernelError(f"expected float32 or bfloat16, got {t.dtype}")
+
+
+def embed(tokens, table, out=None):
+    """h[t] = float32(table[tokens[t]]). tokens int32 [N]; table [V, H] float32|bfloat16."""
+    require(tokens, I32, "embed.tokens")
+    N = tokens.numel()
+    V, H = table.shape
+    if not table.is_contiguous() or not table.is_cuda:
+        raise KernelError("embed.table must be a contiguous CUDA tensor")
+    if out is None:
+        out = torch.empty((N, H), dtype=F32, device=table.device)
+    f = fn("core", "lumen_embed", [P, P, c_int, P, c_int, c_int, c_int, P])
+    check(f(ptr(tokens), ptr(table), _is_bf16(table), ptr(out), N, H, V, stream_ptr()), "embed")
+    return out
+
+
+def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, write_h=True):
+    """x = h + sum(delta[s]) ; y = rmsnorm(x) * weight. h float32 [N, H] (updated in
+    place when write_h); delta None or float32 [S, N, H]; rows int32 [W] gathers."""
+    require(h, F32, "add_rmsnorm.h")
+    require(weight, F32, "add_rmsnorm.weight")
+    N, H = h.shape
+    if weight.numel() != H:
+        raise KernelError(f"add_rmsnorm: weight has {weight.numel()} values, rows have {H}")
+    S, stride = 0, 0
+    if delta is not None:
+        require(delta, F32, "add_rmsnorm.delta")
+        if delta.dim() == 2:
+            delta = delta.unsqueeze(0)
+        if tuple(delta.shape[1:]) != (N, H):
+            raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} does not match h {(N, H)}")
+        S, stride = delta.shape[0], N * H
+    n_rows = N
+    if rows is not None:
+        require(rows, I32, "add_rmsnorm.rows")
+        n_rows = rows.numel()
+    y = torch.empty((n_rows, H), dtype=out_dtype, device=h.device)
+    f = fn("core", "lumen_add_rmsnorm",
+           [P, P, c_int, c_longlong, P, c_float, P, c_int, P, c_int, c_int, c_int, P])
+    check(f(ptr(h), ptr(delta), S, stride, ptr(weight), float(eps), ptr(y), _is_bf16(y), ptr(rows),
+            n_rows, H, 1 if write_h else 0, stream_ptr()), "add_rmsnorm")
+    return y
+
+
+def silu_mul(gu, out_dtype):
+    """z = silu(gu[:, :I]) * gu[:, I:]; gu float32 [N, 2I]."""
+    require(gu, F32, "silu_mul.gu")
+    N, I2 = gu.shape
+    if I2 % 2:
+        raise KernelError("silu_mul: width must be even")
+    z = torch.empty((N, I2 // 2), dtype=out_dtype, device=gu.device)
+    f = fn("core", "lumen_silu_mul", [P, P, c_int, c_int, c_int, P])
+    check(f(ptr(gu), ptr(z), _is_bf16(z), N, I2 // 2, stream_ptr()), "silu_mul")
+    return z
+
+
+def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, rope_pos, cache_pos,
+                       tok_seq, block_table, kcache, vcache, nq, nkv, d, out_dtype):
+    """Per-head RMSNorm of q and k, rotation, q out and k/v written to the paged cache.
+    qkv float32 [N, (nq + 2 nkv) d]; caches [pages, nkv, PAGE, d] of out_dtype
+    (None with nkv == 0: a layer that reads another layer's cache)."""
+    require(qkv, F32, "qk_norm_rope_store.qkv")
+    N = qkv.shape[0]
+    if qkv.shape[1] != (nq + 2 * nkv) * d:
+        raise KernelError(f"qk_norm_rope_store: row width {qkv.shape[1]} != (nq+2nkv)*d")
+    for t, nm in ((q_norm_w, "q_norm"), (k_norm_w, "k_norm")):
+        if t is not None:
+            require(t, F32, nm)
+            if t.numel() != d:
+                raise KernelError(f"{nm} weight must have head_dim={d} values")
+    if rotary_dim:
+        require(inv_freq, F32, "inv_freq")
+        if inv_freq.numel() != rotary_dim // 2:
+            raise KernelError("inv_freq must have rotary_dim/2 values")
+    for t, nm in ((rope_pos, "rope_pos"), (cache_pos, "cache_pos"), (tok_seq, "tok_seq")):
+        require(t, I32, nm)
+        if t.numel() < N:
+            raise KernelError(f"{nm} shorter than the token count")
+    require(block_table, I32, "block_table")
+    q_out = torch.empty((N, nq, d), dtype=out_dtype, device=qkv.device)
+    if nkv:
+        require(kcache, out_dtype, "kcache")
+        require(vcache, out_dtype, "vcache")
+    f = fn("core", "lumen_qk_norm_rope_store",
+           [P, P, P, c_float, P, c_int, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(qkv), ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(inv_freq), int(rotary_dim),
+            ptr(rope_pos), ptr(cache_pos), ptr(tok_seq), ptr(block_table), block_table.stride(0),
+            ptr(q_out), ptr(kcache), ptr(vcache), _is_bf16(q_out), N, nq, nkv, d, stream_ptr()),
+          "qk_norm_rope_store")
+    return q_out
+
+
+def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale):
+    """Causal attention of N query tokens over the paged cache. q [N, nq, d]."""
+    N, nq, d = q.shape
+    nkv = kcache.shape[1]
+    require(q, q.dtype, "attn.q")
+    require(kcache, q.dtype, "attn.kcache")
+    require(vcache, q.dtype, "attn.vcache")
+    require(block_table, I32, "attn.block_table")
+    require(tok_seq, I32, "attn.tok_seq")
+    require(tok_pos, I32, "attn.tok_pos")
+    if d % 16 or d > 256:
+        raise KernelError(f"attention takes head sizes in steps of 16 up to 256, not {d}")
+    out = torch.empty_like(q)
+    f = fn("attn_generic", "lumen_attn_generic",
+           [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P])
+    check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq),
+            ptr(tok_pos), ptr(out), _is_bf16(q), N, nq, nkv, d, int(window), float(scale),
+            stream_ptr()), "attn_generic")
+    return out
+
+
+def gemm_f32(a, w, out=None):
+    """C = a @ w.T in true float32 (FFMA). a float32 [M, K]; w [N, K] float32|bfloat16."""
+    require(a, F32, "gemm_f32.a")
+    M, K = a.shape
+    N, K2 = w.shape
+    if K != K2:
+        raise KernelError(f"gemm_f32: inner sizes differ ({K} vs {K2})")
+    if not (w.is_cuda and w.is_contiguous()):
+        raise KernelError("gemm_f32.w must be a contiguous CUDA tensor")
+    if out is None:
+        out = torch.empty((M, N), dtype=F32, device=a.device)
+    f = fn("gemm_f32", "lumen_gemm_f32", [P, P, c_int, P, c_int, c_int, c_int, P])
+    check(f(ptr(a), ptr(w), _is_bf16(w), ptr(out), M, N, K, stream_ptr()), "gemm_f32")
+    return out
+
+
+def argmax(logits, out=None):
+    """Row-wise argmax of float32 [B, V]; equal maxima give the lowest index."""
+    require(logits, F32, "argmax.logits", contiguous=False)
+    B, V = logits.shape
+    if logits.stride(1) != 1:
+        raise KernelError("argmax: rows must be contiguous")
+    if out is None:
+        out = torch.empty((B,), dtype=I32, device=logits.device)
+    f = fn("sample", "lumen_argmax", [P, c_longlong, c_int, c_int, P, P])
+    check(f(ptr(logits), logits.stride(0), B, V, ptr(out), stream_ptr()), "argmax")
+    return out
+
+
+def sample(logits, opts, top_k, out=None):
+    """Row-wise sampling. opts float32 [B, 4] = (temperature, top_p, min_p, u); top_k int32 [B]."""
+    require(logits, F32, "sample.logits", contiguous=False)
+    require(opts, F32, "sample.opts")
+    require(top_k, I32, "sample.top_k")
+    B, V = logits.shape
+    if logits.stride(1) != 1 or opts.shape != (B, 4) or top_k.numel() != B:
+        raise KernelError("sample: bad shapes")
+    if out is None:
+        out = torch.empty((B,), dtype=I32, device=logits.device)
+    f = fn("sample", "lumen_sample", [P, c_longlong, c_int, c_int, P, P, P, P])
+    check(f(ptr(logits), logits.stride(0), B, V, ptr(opts), ptr(top_k), ptr(out), stream_ptr()),
+          "sample")
+    return out

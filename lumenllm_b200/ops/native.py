@@ -1,0 +1,91 @@
+"""Loads the compiled kernel modules and calls their C entry points.
+
+There is no fallback: if a module cannot be built or loaded, or a launch
+reports an error, an exception says so.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+
+import torch
+
+from ..csrc import build as _build
+
+ERR_UNSUPPORTED = 100001
+ERR_BAD_ARGUMENT = 100002
+ERR_NOT_READY = 100003
+
+
+class KernelError(RuntimeError):
+    pass
+
+
+_libs: dict = {}
+_lock = threading.Lock()
+
+
+def library(module: str) -> ctypes.CDLL:
+    lib = _libs.get(module)
+    if lib is None:
+        with _lock:
+            lib = _libs.get(module)
+            if lib is None:
+                path = _build.ensure_built([module])[module]
+                try:
+                    lib = ctypes.CDLL(str(path))
+                except OSError as e:  # pragma: no cover
+                    raise KernelError(f"cannot load kernel module '{module}' from {path}: {e}") from e
+                _libs[module] = lib
+    return lib
+
+
+def preload(modules) -> None:
+    """Builds (in parallel) and loads the given modules."""
+    _build.ensure_built(list(modules))
+    for m in modules:
+        library(m)
+
+
+_fn_cache: dict = {}
+
+
+def fn(module: str, name: str, argtypes):
+    key = (module, name)
+    f = _fn_cache.get(key)
+    if f is None:
+        f = getattr(library(module), name)
+        f.restype = ctypes.c_int
+        f.argtypes = list(argtypes)
+        _fn_cache[key] = f
+    return f
+
+
+def check(code: int, what: str) -> None:
+    if code == 0:
+        return
+    if code == ERR_UNSUPPORTED:
+        raise KernelError(f"{what}: this kernel does not take these sizes")
+    if code == ERR_BAD_ARGUMENT:
+        raise KernelError(f"{what}: bad argument")
+    if code == ERR_NOT_READY:
+        raise KernelError(f"{what}: the kernel's set-up failed on this device")
+    raise KernelError(f"{what}: CUDA error {code}")
+
+
+def stream_ptr() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def ptr(t):
+    return 0 if t is None else t.data_ptr()
+
+
+def require(t: torch.Tensor, dtype, name: str, *, contiguous=True):
+    if not t.is_cuda:
+        raise KernelError(f"{name}: tensor is not on a CUDA device (no CPU path exists)")
+    if t.dtype != dtype:
+        raise KernelError(f"{name}: expected {dtype}, got {t.dtype}")
+    if contiguous and not t.is_contiguous():
+        raise KernelError(f"{name}: tensor must be contiguous")
+    return t

@@ -1,0 +1,92 @@
+"""The attention mixer: grouped-query causal attention over the cache.
+
+In order (crates/aegisllm-cuda/src/executor/attention.rs:139-202,241-250,341-352,
+413-425; prompt twin executor/prefill/layer.rs:472-636,810-823,967-1047):
+q, k, v = y Wq^T, y Wk^T, y Wv^T; optional per-head RMSNorm of q and k with a
+weight of head_dim values; rotation of q and k; k, v appended to the cache at the
+token's position; for query head h the kv head is h // (heads / kv_heads)
+(attention_decode_common.cuh:112-115), scores scaled by `softmax_scale`, a query
+at position p sees keys j <= p (and p - j < window if a window is set); o = ctx Wo^T.
+Softmax, norms and angles are float32.
+"""
+from __future__ import annotations
+
+import torch
+
+from ..cache.kv import CacheNeed
+from ..ops import kernels as K
+from .base import build_part, need, part_tensors, register_part
+from .linear import Linear
+
+
+@register_part("mixer", "gqa_attention")
+class GQAttention:
+    @classmethod
+    def tensors(cls, spec):
+        p = spec.params
+        H, nq, nkv, d = (int(need(p, k, "gqa_attention")) for k in
+                         ("hidden_size", "num_heads", "num_kv_heads", "head_dim"))
+        t = {f"{spec.prefix}.q_proj.weight": ((nq * d, H), "matrix"),
+             f"{spec.prefix}.o_proj.weight": ((H, nq * d), "matrix")}
+        if not p.get("shares_cache", False):
+            t[f"{spec.prefix}.k_proj.weight"] = ((nkv * d, H), "matrix")
+            t[f"{spec.prefix}.v_proj.weight"] = ((nkv * d, H), "matrix")
+        if p.get("qk_norm", False):
+            t[f"{spec.prefix}.q_norm.weight"] = ((d,), "norm")
+            if not p.get("shares_cache", False):
+                t[f"{spec.prefix}.k_norm.weight"] = ((d,), "norm")
+        t.update(part_tensors("position", p["position"]))
+        return t
+
+    def __init__(self, spec, weights, runtime):
+        p = spec.params
+        self.runtime = runtime
+        self.H = int(p["hidden_size"])
+        self.nq, self.nkv, self.d = int(p["num_heads"]), int(p["num_kv_heads"]), int(p["head_dim"])
+        if self.nq % self.nkv:
+            raise ValueError(f"{self.nq} heads are not a multiple of {self.nkv} kv heads")
+        if self.d % 16 or self.d > 256:
+            raise ValueError(f"head_dim {self.d}: the attention kernels take multiples of 16 up to 256")
+        self.window = int(p.get("window", 0) or 0)
+        self.scale = float(need(p, "softmax_scale", "gqa_attention"))
+        self.shares_cache = bool(p.get("shares_cache", False))
+        self.position = build_part("position", p["position"], weights, runtime)
+        pre = spec.prefix
+        mats = [weights[f"{pre}.q_proj.weight"]]
+        if not self.shares_cache:
+            mats += [weights[f"{pre}.k_proj.weight"], weights[f"{pre}.v_proj.weight"]]
+        self.qkv = Linear.stacked(mats, runtime)
+        # a run that reads another run's cache projects queries only
+        self.q_only = self.qkv if self.shares_cache else \
+            Linear(self.qkv.weight[: self.nq * self.d], runtime)
+        self.o = Linear(weights[f"{pre}.o_proj.weight"], runtime)
+        self.q_norm = self.k_norm = None
+        self.qk_eps = float(p.get("qk_norm_eps", 0.0))
+        if p.get("qk_norm", False):
+            off = float(p.get("qk_norm_weight_offset", 0.0))
+            f32 = lambda n: (weights[n].to(device=runtime.device, dtype=torch.float32) + off).contiguous()
+            self.q_norm = f32(f"{pre}.q_norm.weight")
+            if not self.shares_cache:
+                self.k_norm = f32(f"{pre}.k_norm.weight")
+
+    def cache_need(self):
+        return CacheNeed(self.nkv, self.d, self.window)
+
+    def state_shape(self):
+        return None
+
+    def forward(self, y, ctx, entry):
+        kc, vc, table = entry.cache()
+        writes = entry.writes_cache and not self.shares_cache
+        qkv = self.qkv(y) if writes else self.q_only(y)       # float32 [N, (nq + 2 nkv) d]
+        nkv_new = self.nkv if writes else 0
+        q = K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, self.qk_eps,
+                                 self.position.inv_freq, self.position.rotary_dim,
+                                 ctx.rope_pos, ctx.cache_pos, ctx.tok_seq, table,
+                                 kc if nkv_new else None, vc if nkv_new else None,
+                                 self.nq, nkv_new, self.d, self.runtime.dtype)
+        out = self.attend(q, kc, vc, table, ctx)
+        return self.o(out.view(-1, self.nq * self.d), split_ok=True)
+
+    def attend(self, q, kc, vc, table, ctx):
+        return K.attn_generic(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale)

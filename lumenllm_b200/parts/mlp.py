@@ -1,0 +1,35 @@
+"""Feed-forward parts.
+
+"swiglu": g = y Wg^T, u = y Wu^T, z = g / (1 + exp(-g)) * u, out = z Wd^T
+(crates/aegisllm-cuda/src/executor/mlp.rs:271-356; norm_rope_kv.cu:314-325).
+Gate and up weights are stacked so that both cost one product.
+"""
+from __future__ import annotations
+
+from ..ops import kernels as K
+from .base import need, register_part
+from .linear import Linear
+
+
+@register_part("ffn", "swiglu")
+class SwiGLU:
+    @classmethod
+    def tensors(cls, spec):
+        H = int(need(spec.params, "hidden_size", "swiglu"))
+        I = int(need(spec.params, "intermediate_size", "swiglu"))
+        return {f"{spec.prefix}.gate_proj.weight": ((I, H), "matrix"),
+                f"{spec.prefix}.up_proj.weight": ((I, H), "matrix"),
+                f"{spec.prefix}.down_proj.weight": ((H, I), "matrix")}
+
+    def __init__(self, spec, weights, runtime):
+        self.runtime = runtime
+        pre = spec.prefix
+        self.gate_up = Linear.stacked([weights[f"{pre}.gate_proj.weight"],
+                                       weights[f"{pre}.up_proj.weight"]], runtime)
+        self.down = Linear(weights[f"{pre}.down_proj.weight"], runtime)
+        self.z_dtype = self.runtime.dtype if not self.down.f32 else self.runtime.dtype
+
+    def forward(self, y, ctx):
+        gu = self.gate_up(y)                       # float32 [N, 2I]
+        z = K.silu_mul(gu, self.runtime.dtype)
+        return self.down(z, split_ok=True)
