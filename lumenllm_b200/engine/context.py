@@ -14,9 +14,25 @@ prefill/batch/mod.rs:26-63), for B sequences that bring N tokens together:
 from __future__ import annotations
 
 from dataclasses import dataclass, field
-from typing import Dict, List, Optional
+from typing import Dict, List, Optional, Sequence
 
+import numpy as np
 import torch
+
+from ..cache.kv import pages_for
+
+
+@dataclass
+class StepEntry:
+    """One sequence of a step: its slot, its next tokens, and the places among these
+    tokens whose logits are wanted."""
+    slot: int
+    tokens: Sequence[int]
+    want: Sequence[int] = ()
+
+
+def _pad4(n: int) -> int:
+    return (n + 3) & ~3
 
 
 @dataclass
@@ -75,3 +91,68 @@ class EntryView:
         """Per-sequence state of fixed size: [max_slots, *shape]; row seq_slot[b] belongs
         to sequence b. None if the mixer declared none."""
         return self.ctx.cache.state.of(self.entry)
+
+
+def build_context(cache, runtime, entries, meta_dev=None, pad_to: int = 0, table_width: int = 0):
+    """Reserves cache room and puts the step's metadata on the device. With
+    pad_to > len(entries), padding sequences of one token are appended; they
+    write to the reserved page 0 and are read by nobody."""
+    starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
+    B_real = len(entries)
+    B = max(B_real, pad_to)
+    q_lens = [len(e.tokens) for e in entries] + [1] * (B - B_real)
+    starts_all = starts + [0] * (B - B_real)
+    slots = [e.slot for e in entries] + [-1] * (B - B_real)
+    N = sum(q_lens)
+    W = sum(len(e.want) for e in entries)
+    n_groups = len(cache.groups)
+    width = max(pages_for(s + q) for s, q in zip(starts_all, q_lens))
+    width = max(width, table_width, 1)
+    sizes = [N, N, N, N, B, B, B, B + 1, W] + [B * width] * n_groups
+    offs = np.cumsum([0] + [_pad4(s) for s in sizes])
+    total = int(offs[-1])
+    host = np.zeros((total,), dtype=np.int32)
+    tok = host[offs[0]:offs[0] + N]
+    rpos = host[offs[1]:offs[1] + N]
+    cpos = host[offs[2]:offs[2] + N]
+    tseq = host[offs[3]:offs[3] + N]
+    cu = host[offs[7]:offs[7] + B + 1]
+    want = host[offs[8]:offs[8] + W]
+    n = w = 0
+    for b in range(B):
+        q = q_lens[b]
+        if b < B_real:
+            tok[n:n + q] = np.asarray(entries[b].tokens, dtype=np.int64)
+            for x in entries[b].want:
+                want[w] = n + int(x)
+                w += 1
+        pos = np.arange(starts_all[b], starts_all[b] + q, dtype=np.int32)
+        rpos[n:n + q] = pos
+        cpos[n:n + q] = pos
+        tseq[n:n + q] = b
+        cu[b] = n
+        n += q
+    cu[B] = n
+    host[offs[4]:offs[4] + B] = slots
+    host[offs[5]:offs[5] + B] = starts_all
+    host[offs[6]:offs[6] + B] = q_lens
+    for gi, g in enumerate(cache.groups):
+        bt = host[offs[9 + gi]:offs[9 + gi] + B * width].reshape(B, width)
+        for b in range(B_real):
+            wcols = min(width, g.table.shape[1])
+            bt[b, :wcols] = g.table[slots[b], :wcols]
+    if meta_dev is None or total > meta_dev.numel():
+        grow = max(total, 2 * (0 if meta_dev is None else meta_dev.numel()), 1 << 14)
+        meta_dev = torch.empty((grow,), dtype=torch.int32, device=runtime.device)
+    pinned = torch.from_numpy(host).pin_memory()
+    dev = meta_dev[:total]
+    dev.copy_(pinned, non_blocking=True)
+    sl = lambda i, n_: dev[int(offs[i]):int(offs[i]) + n_]
+    return StepContext(
+        runtime=runtime, B=B, N=N, q_lens=q_lens, starts=starts_all, slots=slots,
+        tokens=sl(0, N), rope_pos=sl(1, N), cache_pos=sl(2, N), tok_seq=sl(3, N),
+        seq_slot=sl(4, B), seq_start=sl(5, B), seq_qlen=sl(6, B), cu_q=sl(7, B + 1),
+        want_rows=sl(8, W),
+        block_tables=[sl(9 + gi, B * width).view(B, width) for gi in range(n_groups)],
+        cache=cache, n_real=B_real), meta_dev
+

@@ -23,7 +23,7 @@ from ..cache.kv import PAGE, KVCache, pages_for
 from ..cache.slots import CacheError, CacheFull
 from ..config import ConfigError, ModelSpec, load_config
 from ..parts.base import Runtime
-from .context import StepContext
+from .context import StepContext, StepEntry, build_context
 from .model import DecoderModel, expected_tensors
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32,
@@ -32,17 +32,6 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32,
 
 class StepError(ValueError):
     """A step was refused before anything ran."""
-
-
-@dataclass
-class StepEntry:
-    slot: int
-    tokens: Sequence[int]
-    want: Sequence[int] = ()
-
-
-def _pad4(n: int) -> int:
-    return (n + 3) & ~3
 
 
 def require_gpu(device=None) -> torch.device:
@@ -55,7 +44,7 @@ def require_gpu(device=None) -> torch.device:
 class Engine:
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], dtype="bfloat16",
                  max_tokens: int = 8192, max_slots: Optional[int] = None, device=None,
-                 config=None):
+                 config=None, context_size: Optional[int] = None, max_step_tokens: int = 8192):
         if dtype not in _DTYPES:
             raise ConfigError(f"dtype {dtype!r}: bfloat16 or float32")
         self.device = require_gpu(device)
@@ -71,12 +60,17 @@ class Engine:
                              dtype=self.runtime.dtype, device=self.device,
                              state_shapes=self.model.state_shapes())
         self.vocab_size = spec.vocab_size
+        self.max_seq_len = min(spec.max_positions, context_size or spec.max_positions)
+        self.max_step_tokens = max(1, int(max_step_tokens))
+        from ..sampling import DeviceSampler
+        self.sampler = DeviceSampler(self.device)
         self._meta_dev = torch.empty((1 << 16,), dtype=torch.int32, device=self.device)
         self.steps_run = 0
 
     # ------------------------------------------------------------ construction
     @classmethod
-    def from_folder(cls, folder, dtype="bfloat16", max_tokens=8192, max_slots=None, device=None):
+    def from_folder(cls, folder, dtype="bfloat16", max_tokens=8192, max_slots=None, device=None,
+                    **kw):
         """A folder with config.json and model.safetensors; config.json chooses the model."""
         from ..weights import load_weights
         dev = require_gpu(device)
@@ -84,11 +78,11 @@ class Engine:
         spec = config.model_spec()
         exp = {n: shape for n, (shape, _) in expected_tensors(spec).items()}
         weights = load_weights(folder, exp, dev)
-        return cls(spec, weights, dtype, max_tokens, max_slots, dev.index, config=config)
+        return cls(spec, weights, dtype, max_tokens, max_slots, dev.index, config=config, **kw)
 
     @classmethod
     def from_random(cls, config, seed=0, std=0.02, norm_jitter=0.0, dtype="bfloat16",
-                    max_tokens=8192, max_slots=None, device=None, weight_dtype="bfloat16"):
+                    max_tokens=8192, max_slots=None, device=None, weight_dtype="bfloat16", **kw):
         """Random weights made on the device (large shapes need no file)."""
         from ..config import config_from_dict
         from ..weights import random_weights
@@ -98,7 +92,7 @@ class Engine:
         spec = config.model_spec()
         weights = random_weights(expected_tensors(spec), seed, std, norm_jitter,
                                  _DTYPES[weight_dtype], device=dev)
-        return cls(spec, weights, dtype, max_tokens, max_slots, dev.index, config=config)
+        return cls(spec, weights, dtype, max_tokens, max_slots, dev.index, config=config, **kw)
 
     # ------------------------------------------------------------ slots
     def alloc_slot(self) -> int:
@@ -132,79 +126,37 @@ class Engine:
                 if not 0 <= int(w) < len(e.tokens):
                     raise StepError(f"slot {e.slot}: wanted place {w} is not among the "
                                     f"{len(e.tokens)} tokens of this step")
-            if self.cache.length(e.slot) + len(e.tokens) > self.spec.max_positions:
-                raise StepError(f"slot {e.slot}: {self.cache.length(e.slot) + len(e.tokens)} tokens "
-                                f"exceed max_position_embeddings {self.spec.max_positions}")
+            if self.cache.length(e.slot) + len(e.tokens) > self.max_seq_len:
+                raise StepError(f"slot {e.slot}: kv cache context exhausted: "
+                                f"{self.cache.length(e.slot) + len(e.tokens)} tokens exceed the "
+                                f"context size {self.max_seq_len}")
 
     def build_context(self, entries: Sequence[StepEntry], pad_to: int = 0,
                       table_width: int = 0) -> StepContext:
-        """Reserves cache room and puts the step's metadata on the device. With
-        pad_to > len(entries), padding sequences of one token are appended; they
-        write to the reserved page 0 and are read by nobody."""
-        starts = [self.cache.reserve(e.slot, len(e.tokens)) for e in entries]
-        B_real = len(entries)
-        B = max(B_real, pad_to)
-        q_lens = [len(e.tokens) for e in entries] + [1] * (B - B_real)
-        starts_all = starts + [0] * (B - B_real)
-        slots = [e.slot for e in entries] + [-1] * (B - B_real)
-        N = sum(q_lens)
-        W = sum(len(e.want) for e in entries)
-        n_groups = len(self.cache.groups)
-        width = max(pages_for(s + q) for s, q in zip(starts_all, q_lens))
-        width = max(width, table_width, 1)
-        sizes = [N, N, N, N, B, B, B, B + 1, W] + [B * width] * n_groups
-        offs = np.cumsum([0] + [_pad4(s) for s in sizes])
-        total = int(offs[-1])
-        host = np.zeros((total,), dtype=np.int32)
-        tok = host[offs[0]:offs[0] + N]
-        rpos = host[offs[1]:offs[1] + N]
-        cpos = host[offs[2]:offs[2] + N]
-        tseq = host[offs[3]:offs[3] + N]
-        cu = host[offs[7]:offs[7] + B + 1]
-        want = host[offs[8]:offs[8] + W]
-        n = w = 0
-        for b in range(B):
-            q = q_lens[b]
-            if b < B_real:
-                tok[n:n + q] = np.asarray(entries[b].tokens, dtype=np.int64)
-                for x in entries[b].want:
-                    want[w] = n + int(x)
-                    w += 1
-            pos = np.arange(starts_all[b], starts_all[b] + q, dtype=np.int32)
-            rpos[n:n + q] = pos
-            cpos[n:n + q] = pos
-            tseq[n:n + q] = b
-            cu[b] = n
-            n += q
-        cu[B] = n
-        host[offs[4]:offs[4] + B] = slots
-        host[offs[5]:offs[5] + B] = starts_all
-        host[offs[6]:offs[6] + B] = q_lens
-        for gi, g in enumerate(self.cache.groups):
-            bt = host[offs[9 + gi]:offs[9 + gi] + B * width].reshape(B, width)
-            for b in range(B_real):
-                wcols = min(width, g.table.shape[1])
-                bt[b, :wcols] = g.table[slots[b], :wcols]
-        if total > self._meta_dev.numel():
-            self._meta_dev = torch.empty((max(total, 2 * self._meta_dev.numel()),),
-                                         dtype=torch.int32, device=self.device)
-        pinned = torch.from_numpy(host).pin_memory()
-        dev = self._meta_dev[:total]
-        dev.copy_(pinned, non_blocking=True)
-        sl = lambda i, n_: dev[int(offs[i]):int(offs[i]) + n_]
-        return StepContext(
-            runtime=self.runtime, B=B, N=N, q_lens=q_lens, starts=starts_all, slots=slots,
-            tokens=sl(0, N), rope_pos=sl(1, N), cache_pos=sl(2, N), tok_seq=sl(3, N),
-            seq_slot=sl(4, B), seq_start=sl(5, B), seq_qlen=sl(6, B), cu_q=sl(7, B + 1),
-            want_rows=sl(8, W),
-            block_tables=[sl(9 + gi, B * width).view(B, width) for gi in range(n_groups)],
-            cache=self.cache, n_real=B_real)
+        ctx, self._meta_dev = build_context(self.cache, self.runtime, entries, self._meta_dev,
+                                            pad_to=pad_to, table_width=table_width)
+        return ctx
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs the given tokens; returns float32 logits [wanted, vocab] on the device, in
         the order of the entries and of their `want`."""
-        entries = list(entries)
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         self._validate(entries)
+        if sum(len(e.tokens) for e in entries) <= self.max_step_tokens:
+            return self._forward(entries)
+        # More tokens than one pass may hold in activations: the same work in several
+        # passes over the same cache. Pieces of one sequence run in order, so every
+        # token still sees exactly the keys before it.
+        parts, origin = self._split(entries)
+        out = [self._forward(p) for p in parts]
+        logits = torch.cat(out, dim=0)
+        if origin != sorted(origin):
+            order = torch.tensor(sorted(range(len(origin)), key=origin.__getitem__),
+                                 dtype=torch.long, device=logits.device)
+            logits = logits.index_select(0, order)
+        return logits
+
+    def _forward(self, entries: List[StepEntry]) -> torch.Tensor:
         try:
             ctx = self.build_context(entries)
         except CacheFull as e:
@@ -214,3 +166,55 @@ class Engine:
             self.cache.commit(e.slot, len(e.tokens))
         self.steps_run += 1
         return logits
+
+    def _split(self, entries: List[StepEntry]):
+        """Cuts a step into passes of at most max_step_tokens tokens. Returns the passes
+        and, for every output row in pass order, its index in the caller's order."""
+        budget = self.max_step_tokens
+        row0, rows = 0, []
+        for e in entries:
+            rows.append({int(w): [] for w in e.want})
+            for k, w in enumerate(e.want):
+                rows[-1][int(w)].append(row0 + k)
+            row0 += len(e.want)
+        parts, origin, cur, room = [], [], [], budget
+        for ei, e in enumerate(entries):
+            toks = list(e.tokens)
+            off = 0
+            while off < len(toks):
+                if room == 0:
+                    parts.append(cur)
+                    cur, room = [], budget
+                n = min(room, len(toks) - off)
+                want_here = sorted(w for w in rows[ei] if off <= w < off + n)
+                wl = []
+                for w in want_here:
+                    for gi in rows[ei][w]:
+                        wl.append(w - off)
+                        origin.append(gi)
+                cur.append(StepEntry(e.slot, toks[off:off + n], wl))
+                off += n
+                room -= n
+                if off < len(toks):   # the rest of this sequence needs a later pass
+                    parts.append(cur)
+                    cur, room = [], budget
+        if cur:
+            parts.append(cur)
+        return parts, origin
+
+    # ------------------------------------------------------------ generation
+    def run(self, entries, configs, uniforms) -> List[int]:
+        """Backend face of the generation loop: feeds each (slot, tokens), samples one
+        token per sequence from the logits at its last token, returns them on the host."""
+        logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in entries])
+        return self.sampler.pick(logits, configs, uniforms).tolist()
+
+    def generate(self, requests, eos_token_ids=None, max_batch: int = 64, on_token=None):
+        """`requests`: one GenerateRequest or a list. Returns GenerateOutput(s)."""
+        from .generate import GenerateRequest, generate
+        single = isinstance(requests, GenerateRequest)
+        reqs = [requests] if single else list(requests)
+        eos = self.spec.eos_token_ids if eos_token_ids is None else eos_token_ids
+        outs = generate(self, reqs, eos, max_batch=min(max_batch, self.cache.max_slots),
+                        token_budget=self.cache.n_pages * PAGE, on_token=on_token)
+        return outs[0] if single else outs

@@ -1,0 +1,3 @@
+from .sampler import DeviceSampler, SamplingConfig, fresh_seed, uniform
+
+__all__ = ["DeviceSampler", "SamplingConfig", "fresh_seed", "uniform"]

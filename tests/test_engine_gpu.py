@@ -1,0 +1,325 @@
+"""The engine against the plain implementation, in float32 and in bfloat16: each request
+alone and whole; with the last 32 tokens one by one; in batches of unequal lengths whose
+shorter requests end earlier, one batch after another so that slots and pages are used
+again; long decoding; the first tokens of a sequence; generation through the entry point;
+the replay tool as a program."""
+import json
+import os
+import subprocess
+import sys
+from pathlib import Path
+
+import numpy as np
+import pytest
+import torch
+
+import plain_qwen3 as P
+from conftest import ROOT, TINY, seeded_tokens, tolerance
+
+pytestmark = pytest.mark.gpu
+
+DTYPES = ["float32", "bfloat16"]
+NAMES = ["A", "B", "C"]
+
+
+@pytest.fixture(scope="module")
+def plain(tiny_models):
+    return {n: P.load_model(tiny_models[n]) for n in NAMES}
+
+
+@pytest.fixture(scope="module")
+def engines(tiny_models):
+    from lumenllm_b200 import Engine
+    cache = {}
+
+    def get(name, dtype, max_tokens=4096):
+        key = (name, dtype, max_tokens)
+        if key not in cache:
+            cache[key] = Engine.from_folder(tiny_models[name], dtype=dtype, max_tokens=max_tokens)
+        return cache[key]
+    return get
+
+
+def run_whole(eng, seq):
+    from lumenllm_b200 import StepEntry
+    s = eng.alloc_slot()
+    lg = eng.step([StepEntry(s, seq, list(range(len(seq))))]).cpu()
+    eng.free_slot(s)
+    return lg
+
+
+def run_tail(eng, seq, tail=32):
+    from lumenllm_b200 import StepEntry
+    s = eng.alloc_slot()
+    cut = max(1, len(seq) - tail)
+    out = [eng.step([StepEntry(s, seq[:cut], list(range(cut)))]).cpu()]
+    for t in seq[cut:]:
+        out.append(eng.step([StepEntry(s, [t], [0])]).cpu())
+    eng.free_slot(s)
+    return torch.cat(out)
+
+
+def run_batch(eng, seqs, prompt_lens):
+    """All prompts in one step, then one token each; a finished request leaves at once."""
+    from lumenllm_b200 import StepEntry
+    slots = [eng.alloc_slot() for _ in seqs]
+    lg = eng.step([StepEntry(s, q[:c], list(range(c))) for s, q, c in zip(slots, seqs, prompt_lens)]).cpu()
+    got, o = [], 0
+    for c in prompt_lens:
+        got.append([lg[o:o + c]])
+        o += c
+    pos = list(prompt_lens)
+    live = list(range(len(seqs)))
+    while True:
+        for i in [i for i in live if pos[i] >= len(seqs[i])]:
+            eng.free_slot(slots[i])
+        live = [i for i in live if pos[i] < len(seqs[i])]
+        if not live:
+            break
+        lg = eng.step([StepEntry(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu()
+        for k, i in enumerate(live):
+            got[i].append(lg[k:k + 1])
+            pos[i] += 1
+    return [torch.cat(g) for g in got]
+
+
+def check(got, ref, dtype, what):
+    assert got.shape == ref.shape, what
+    assert torch.isfinite(got).all(), what
+    err = float((got - ref).abs().max())
+    tol = tolerance(dtype, ref)
+    if err > tol:
+        bad = int((got - ref).abs().max(dim=1).values.argmax())
+        raise AssertionError(f"{what}: max abs error {err:.3e} > {tol:.3e}; worst position {bad} "
+                             f"of {got.shape[0]}")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_whole_tail_and_batches(name, dtype, plain, engines):
+    cfg, w = plain[name]
+    eng = engines(name, dtype)
+    lens = [7, 1, 19, 150, 70, 33, 2, 64, 11, 129]
+    seqs = seeded_tokens(cfg["vocab_size"], lens, 100 + ord(name))
+    refs = [P.forward_logits(cfg, w, s) for s in seqs]
+    for s, r in zip(seqs, refs):
+        check(run_whole(eng, s), r, dtype, f"{name} whole len {len(s)}")
+    for s, r in zip(seqs, refs):
+        check(run_tail(eng, s), r, dtype, f"{name} tail32 len {len(s)}")
+    # batches of unequal lengths, one after another on the same engine
+    for batch in ([0, 1, 2], [3, 4, 5, 6], [7, 8, 9, 0, 3]):
+        bs = [seqs[i] for i in batch]
+        cuts = [max(1, (len(s) * 2) // 3) for s in bs]
+        for g, i in zip(run_batch(eng, bs, cuts), batch):
+            check(g, refs[i], dtype, f"{name} batch {batch} request {i}")
+        eng.cache.check()
+    assert not eng.cache.slots.held
+    for g in eng.cache.groups:
+        assert g.pool.free_count == g.pool.capacity
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_slots_and_pages_used_again_hold_no_stale_keys(dtype, plain, tiny_models):
+    """A cache just large enough: every page of the second batch was used by the first."""
+    from lumenllm_b200 import Engine
+    cfg, w = plain["B"]
+    eng = Engine.from_folder(tiny_models["B"], dtype=dtype, max_tokens=4 * 64, max_slots=2)
+    seqs = seeded_tokens(cfg["vocab_size"], [100, 120, 90, 128, 5, 70], 7)
+    refs = [P.forward_logits(cfg, w, s) for s in seqs]
+    for pair in ([0, 1], [2, 3], [4, 5], [1, 2]):
+        bs = [seqs[i] for i in pair]
+        for g, i in zip(run_batch(eng, bs, [len(s) // 2 for s in bs]), pair):
+            check(g, refs[i], dtype, f"reuse pair {pair} request {i}")
+        eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["A", "C"])
+def test_long_decoding(name, dtype, plain, engines):
+    """3 prompt tokens, then 400 single tokens: page edges, the 128-key chunk edges of the
+    attention kernels, and for C the window sliding over page edges."""
+    cfg, w = plain[name]
+    seq = seeded_tokens(cfg["vocab_size"], [403], 21)[0]
+    ref = P.forward_logits(cfg, w, seq)
+    check(run_tail(engines(name, dtype), seq, tail=400), ref, dtype, f"{name} long decode")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_first_tokens(name, dtype, plain, engines):
+    from lumenllm_b200 import StepEntry
+    cfg, w = plain[name]
+    eng = engines(name, dtype)
+    seqs = seeded_tokens(cfg["vocab_size"], [1, 2, 3, 1], 31)
+    refs = [P.forward_logits(cfg, w, s) for s in seqs]
+    slots = [eng.alloc_slot() for _ in seqs]
+    # token by token from the very first one, all four together
+    for t in range(3):
+        live = [i for i in range(4) if t < len(seqs[i])]
+        lg = eng.step([StepEntry(slots[i], [seqs[i][t]], [0]) for i in live]).cpu()
+        for k, i in enumerate(live):
+            check(lg[k:k + 1], refs[i][t:t + 1], dtype, f"{name} first tokens, request {i} place {t}")
+    for s in slots:
+        eng.free_slot(s)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_want_selects_rows_and_may_be_empty(dtype, plain, engines):
+    from lumenllm_b200 import StepEntry
+    cfg, w = plain["B"]
+    eng = engines("B", dtype)
+    a, b = seeded_tokens(cfg["vocab_size"], [20, 9], 41)
+    ra, rb = P.forward_logits(cfg, w, a), P.forward_logits(cfg, w, b)
+    sa, sb = eng.alloc_slot(), eng.alloc_slot()
+    lg = eng.step([StepEntry(sa, a[:10], []), StepEntry(sb, b, [8, 0])]).cpu()
+    assert lg.shape[0] == 2
+    check(lg, torch.stack([rb[8], rb[0]]), dtype, "want order")
+    assert eng.step([StepEntry(sa, a[10:15], [])]).shape[0] == 0
+    lg = eng.step([StepEntry(sa, a[15:], [4])]).cpu()
+    check(lg, ra[19:20], dtype, "after steps that wanted nothing")
+    eng.free_slot(sa); eng.free_slot(sb)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_padding_changes_nothing(dtype, plain, engines):
+    from lumenllm_b200 import StepEntry
+    cfg, w = plain["A"]
+    eng = engines("A", dtype)
+    a, b = seeded_tokens(cfg["vocab_size"], [30, 5], 51)
+    outs = []
+    for pad in (0, 8):
+        sa, sb = eng.alloc_slot(), eng.alloc_slot()
+        eng.step([StepEntry(sa, a[:-1], []), StepEntry(sb, b[:-1], [])])
+        entries = [StepEntry(sa, a[-1:], [0]), StepEntry(sb, b[-1:], [0])]
+        ctx = eng.build_context(entries, pad_to=pad)
+        outs.append(eng.model.forward(ctx).cpu())
+        eng.free_slot(sa); eng.free_slot(sb)
+    assert torch.equal(outs[0], outs[1])
+    ref = torch.stack([P.forward_logits(cfg, w, a)[-1], P.forward_logits(cfg, w, b)[-1]])
+    check(outs[1], ref, dtype, "padded step")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_large_step_is_cut_into_passes(dtype, plain, tiny_models):
+    from lumenllm_b200 import Engine, StepEntry
+    cfg, w = plain["A"]
+    eng = Engine.from_folder(tiny_models["A"], dtype=dtype, max_tokens=1024, max_step_tokens=37)
+    seqs = seeded_tokens(cfg["vocab_size"], [90, 10, 41], 61)
+    slots = [eng.alloc_slot() for _ in seqs]
+    wants = [[89, 0, 40], [9], [40, 36, 37]]
+    lg = eng.step([StepEntry(s, q, wt) for s, q, wt in zip(slots, seqs, wants)]).cpu()
+    ref = torch.cat([P.forward_logits(cfg, w, q)[wt] for q, wt in zip(seqs, wants)])
+    check(lg, ref, dtype, "cut step")
+
+
+def test_refused_steps(engines):
+    from lumenllm_b200 import StepEntry, StepError
+    eng = engines("A", "float32")
+    s = eng.alloc_slot()
+    for bad, msg in (([], "at least one sequence"),
+                     ([StepEntry(s, [], [])], "at least one token"),
+                     ([StepEntry(s, [256], [])], "outside the vocabulary"),
+                     ([StepEntry(s, [-1], [])], "outside the vocabulary"),
+                     ([StepEntry(s, [1], [1])], "wanted place"),
+                     ([StepEntry(s, [1], []), StepEntry(s, [2], [])], "twice"),
+                     ([StepEntry(999, [1], [])], "not live"),
+                     ([StepEntry(s, [1] * 1025, [])], "context")):
+        with pytest.raises(StepError, match=msg):
+            eng.step(bad)
+    assert eng.length(s) == 0
+    eng.free_slot(s)
+    small = engines("A", "float32", 128)
+    a, b = small.alloc_slot(), small.alloc_slot()
+    small.step([StepEntry(a, [1] * 100, [])])
+    with pytest.raises(StepError, match=f"slot {b}.*full"):
+        small.step([StepEntry(b, [1] * 100, [])])
+    small.free_slot(a); small.free_slot(b)
+
+
+def _teacher_check(cfg, w, prompt, produced, dtype):
+    """Every produced token is the plain implementation's choice given the same prefix,
+    or ties with it within the tolerance."""
+    lg = P.forward_logits(cfg, w, list(prompt) + list(produced))
+    for k, tok in enumerate(produced):
+        row = lg[len(prompt) - 1 + k]
+        assert float(row.max() - row[tok]) <= 2 * tolerance(dtype, row), (k, tok)
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_greedy_generation_through_the_entry_point(name, dtype, plain, tiny_models):
+    from lumenllm_b200 import EngineConfig, GenerateRequest, build
+    cfg, w = plain[name]
+    built = build(EngineConfig(model_path=str(tiny_models[name]), dtype=dtype, context_size=256,
+                               max_batch=3))
+    lens = [7, 1, 19] if name == "A" else [33, 2, 64, 11]
+    steps = 8 if name == "A" else 12
+    prompts = seeded_tokens(cfg["vocab_size"], lens, 71)
+    outs = built.generate([GenerateRequest(p, steps) for p in prompts], eos_token_ids=[])
+    for p, o in zip(prompts, outs):
+        assert o.finish_reason == "length" and o.completion_tokens == steps
+        _teacher_check(cfg, w, p, o.tokens, dtype)
+        if dtype == "float32":
+            assert o.tokens == P.generate_greedy(cfg, w, p, steps)[0]
+    # stop and eos, decided from the tokens the first run produced
+    first = outs[0].tokens
+    o2 = built.generate(GenerateRequest(prompts[0], steps, stop_token_ids=[first[3]]), eos_token_ids=[])
+    assert o2.tokens == first[:first.index(first[3]) + 1] and o2.finish_reason == "stop"
+    o3 = built.generate(GenerateRequest(prompts[0], steps), eos_token_ids=[first[2]])
+    assert o3.tokens == first[:first.index(first[2])] and o3.finish_reason == "eos_token"
+    built.engine.cache.check()
+    assert not built.engine.cache.slots.held
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_seeded_sampling_alone_and_in_a_batch(dtype, plain, tiny_models):
+    from lumenllm_b200 import EngineConfig, GenerateRequest, SamplingConfig, build
+    cfg, w = plain["B"]
+    built = build(EngineConfig(model_path=str(tiny_models["B"]), dtype=dtype, context_size=256,
+                               max_batch=4))
+    prompts = seeded_tokens(cfg["vocab_size"], [33, 2, 64, 11], 81)
+    sc = [SamplingConfig(temperature=0.8, seed=1000 + i) for i in range(4)]
+    together = built.generate([GenerateRequest(p, 12, s) for p, s in zip(prompts, sc)], eos_token_ids=[])
+    again = built.generate([GenerateRequest(p, 12, s) for p, s in zip(prompts, sc)], eos_token_ids=[])
+    assert [o.tokens for o in together] == [o.tokens for o in again]
+    if dtype == "float32":
+        for p, s, o in zip(prompts, sc, together):
+            alone = built.generate(GenerateRequest(p, 12, s), eos_token_ids=[])
+            assert alone.tokens == o.tokens
+    other = built.generate(GenerateRequest(prompts[0], 12, SamplingConfig(temperature=0.8, seed=5)),
+                           eos_token_ids=[])
+    assert other.tokens != together[0].tokens
+
+
+def test_trace_run_program(tmp_path, plain, tiny_models):
+    """bin/trace_run as a program: whole prompts of a batch, then single tokens, a request
+    that ends earlier, then a second batch on the slots of the first."""
+    cfg, w = plain["B"]
+    a, b, c = seeded_tokens(cfg["vocab_size"], [40, 9, 70], 91)
+    steps = [
+        {"step": 0, "entries": [{"id": "a", "tokens": a[:30], "want": [0, 29]},
+                                {"id": "b", "tokens": b[:8], "want": [7]}], "end": []},
+        {"step": 1, "entries": [{"id": "a", "tokens": [a[30]], "want": [0]},
+                                {"id": "b", "tokens": [b[8]], "want": [0]}], "end": ["b"]},
+        {"step": 2, "entries": [{"id": "a", "tokens": [a[31]], "want": []}], "end": []},
+        {"step": 3, "entries": [{"id": "a", "tokens": [a[32]], "want": [0]}], "end": ["a"]},
+        {"step": 4, "entries": [{"id": "c", "tokens": c, "want": [69]}], "end": ["c"]},
+    ]
+    for dtype in DTYPES:
+        out = tmp_path / dtype
+        env = dict(os.environ)
+        proc = subprocess.run([sys.executable, str(ROOT / "bin" / "trace_run"), "--model",
+                               str(tiny_models["B"]), "--dtype", dtype, "--out", str(out),
+                               "--max-tokens", "128"],
+                              input="\n".join(json.dumps(s) for s in steps) + "\n", text=True,
+                              capture_output=True, env=env, timeout=600)
+        assert proc.returncode == 0, proc.stderr[-2000:]
+        assert proc.stdout.split() == ["done", "0", "done", "1", "done", "2", "done", "3", "done", "4"]
+        ra, rb, rc = (P.forward_logits(cfg, w, s) for s in (a, b, c))
+        V = cfg["vocab_size"]
+        rd = lambda k: torch.from_numpy(np.fromfile(out / f"{k}.f32", dtype="<f4").reshape(-1, V))
+        check(rd(0), torch.stack([ra[0], ra[29], rb[7]]), dtype, "trace step 0")
+        check(rd(1), torch.stack([ra[30], rb[8]]), dtype, "trace step 1")
+        assert not (out / "2.f32").exists()
+        check(rd(3), ra[32:33], dtype, "trace step 3")
+        check(rd(4), rc[69:70], dtype, "trace step 4")

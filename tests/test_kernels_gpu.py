@@ -1,0 +1,297 @@
+"""Each kernel alone against a plain float32 reference of the same operation, at sizes other
+than the tiny models': widths and vocabularies that are no power of two, head sizes in steps
+of 16, odd numbers of heads and groups, lengths that cross page and chunk edges, and inputs
+made so that a single far key, a window's edge or a page of the cache decides the result."""
+import math
+
+import pytest
+import torch
+
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+
+F32, BF16, I32 = torch.float32, torch.bfloat16, torch.int32
+
+
+def dev(t):
+    return t.cuda()
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_embed(dtype):
+    from lumenllm_b200.ops import kernels as K
+    V, H = 311, 1000
+    table = torch.randn(V, H, generator=gen(0)).to(dtype)
+    tok = torch.tensor([0, 310, 5, 5, 17], dtype=I32)
+    out = K.embed(dev(tok), dev(table)).cpu()
+    assert torch.equal(out, table[tok.long()].float())
+
+
+@pytest.mark.parametrize("out_dtype", [F32, BF16])
+@pytest.mark.parametrize("H,S", [(1000, 0), (80, 1), (4096 + 48, 3)])
+def test_add_rmsnorm(out_dtype, H, S):
+    from lumenllm_b200.ops import kernels as K
+    N, eps = 13, 1e-5
+    g = gen(1)
+    h = torch.randn(N, H, generator=g)
+    w = 1 + 0.1 * torch.randn(H, generator=g)
+    delta = torch.randn(S, N, H, generator=g) if S else None
+    x = h.clone()
+    for s in range(S):
+        x = x + delta[s]
+    ref = P.rms_norm(x, w, eps)
+    hd = dev(h.clone())
+    y = K.add_rmsnorm(hd, dev(delta) if S else None, dev(w), eps, out_dtype).cpu().float()
+    tol = 1e-5 if out_dtype == F32 else 2 ** -8
+    assert float(((y - ref).abs() / (1 + ref.abs())).max()) < tol
+    assert torch.allclose(hd.cpu(), x, atol=1e-6)             # the stream took the update
+    # gathered rows, stream untouched
+    rows = torch.tensor([12, 0, 7], dtype=I32)
+    hd2 = dev(h.clone())
+    y2 = K.add_rmsnorm(hd2, dev(delta) if S else None, dev(w), eps, out_dtype, rows=dev(rows),
+                       write_h=False).cpu().float()
+    assert float(((y2 - ref[rows.long()]).abs() / (1 + ref[rows.long()].abs())).max()) < tol
+    assert torch.equal(hd2.cpu(), h)
+
+
+@pytest.mark.parametrize("out_dtype", [F32, BF16])
+def test_silu_mul(out_dtype):
+    from lumenllm_b200.ops import kernels as K
+    N, I = 7, 176
+    gu = torch.randn(N, 2 * I, generator=gen(2)) * 3
+    ref = P.swiglu(gu[:, :I], gu[:, I:])
+    z = K.silu_mul(dev(gu), out_dtype).cpu().float()
+    tol = 1e-6 if out_dtype == F32 else 2 ** -8
+    assert float(((z - ref).abs() / (1 + ref.abs())).max()) < tol
+
+
+def _paged(T, nkv, d, dtype, n_pages, seed):
+    """A page table that walks the pool backwards with a gap, so that position order and
+    page order differ."""
+    need = (T + 63) // 64
+    pages = list(range(n_pages - 1, 0, -2))[:need]
+    assert len(pages) == need
+    k = torch.zeros(n_pages, nkv, 64, d, dtype=dtype)
+    v = torch.zeros(n_pages, nkv, 64, d, dtype=dtype)
+    return pages, k, v
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("nq,nkv,d,rot", [(6, 3, 48, 48), (5, 5, 16, 8), (8, 2, 128, 128), (3, 1, 80, 80)])
+def test_qk_norm_rope_store(dtype, nq, nkv, d, rot):
+    from lumenllm_b200.ops import kernels as K
+    g = gen(3)
+    lens = [70, 3]                         # two sequences; the first starts at position 60
+    starts = [60, 0]
+    N = sum(lens)
+    qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g)
+    qw = 1 + 0.1 * torch.randn(d, generator=g)
+    kw = 1 + 0.1 * torch.randn(d, generator=g)
+    theta, eps = 50000.0, 1e-6
+    inv = P.rope_inv_freq(d, theta, rot)
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(I32)
+    seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).to(I32)
+    n_pages = 12
+    table = torch.tensor([[9, 4, 7], [2, 0, 0]], dtype=I32)
+    kc = torch.zeros(n_pages, nkv, 64, d, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    kcd, vcd = dev(kc), dev(vc)
+    q = K.qk_norm_rope_store(dev(qkv), dev(qw), dev(kw), eps, dev(inv), rot, dev(pos), dev(pos),
+                             dev(seq), dev(table), kcd, vcd, nq, nkv, d, dtype).cpu().float()
+    x = qkv.view(N, nq + 2 * nkv, d)
+    qr = P.apply_rope(P.rms_norm(x[:, :nq], qw, eps), pos, theta, rot)
+    kr = P.apply_rope(P.rms_norm(x[:, nq:nq + nkv], kw, eps), pos, theta, rot)
+    vr = x[:, nq + nkv:]
+    tol = 2e-6 if dtype == F32 else 2 ** -8
+    rel = lambda a, b: float(((a - b).abs() / (1 + b.abs())).max())
+    assert rel(q, qr) < tol
+    kg, vg = kcd.cpu().float(), vcd.cpu().float()
+    for n in range(N):
+        pg = int(table[seq[n], pos[n] // 64])
+        assert rel(kg[pg, :, pos[n] % 64], kr[n]) < tol
+        assert rel(vg[pg, :, pos[n] % 64], vr[n]) < tol
+    # nothing else was written: untouched pages stay zero
+    used = {int(table[seq[n], pos[n] // 64]) for n in range(N)}
+    for pg in range(n_pages):
+        if pg not in used:
+            assert float(kg[pg].abs().max()) == 0.0
+    # without norm weights and without rotation the values pass through
+    q2 = K.qk_norm_rope_store(dev(qkv), None, None, eps, None, 0, dev(pos), dev(pos), dev(seq),
+                              dev(table), kcd, vcd, nq, nkv, d, dtype).cpu().float()
+    assert rel(q2, x[:, :nq]) < tol
+
+
+def _attn_case(lens, starts, nq, nkv, d, dtype, window, seed, n_pages=40):
+    """Builds paged caches holding `starts[b] + lens[b]` positions for each sequence and
+    queries for the last lens[b] positions; returns kernel inputs and the plain result."""
+    g = gen(seed)
+    B = len(lens)
+    totals = [s + n for s, n in zip(starts, lens)]
+    width = max((t + 63) // 64 for t in totals)
+    table = torch.zeros(B, width, dtype=I32)
+    free = list(range(n_pages - 1, 0, -1))
+    ks, vs = [], []
+    kc = torch.zeros(n_pages, nkv, 64, d)
+    vc = torch.zeros_like(kc)
+    for b, t in enumerate(totals):
+        k = torch.randn(t, nkv, d, generator=g)
+        v = torch.randn(t, nkv, d, generator=g)
+        ks.append(k); vs.append(v)
+        for p in range((t + 63) // 64):
+            pg = free.pop(3 if len(free) > 3 else 0)     # not in order
+            table[b, p] = pg
+            n = min(64, t - 64 * p)
+            kc[pg, :, :n] = k[64 * p:64 * p + n].transpose(0, 1)
+            vc[pg, :, :n] = v[64 * p:64 * p + n].transpose(0, 1)
+    qs = [torch.randn(n, nq, d, generator=g) for n in lens]
+    return table, kc, vc, ks, vs, qs
+
+
+def _attn_ref(qs, ks, vs, lens, starts, window, dtype):
+    outs = []
+    for q, k, v, n, s in zip(qs, ks, vs, lens, starts):
+        k, v, q = (x.to(dtype).float() for x in (k, v, q))
+        T = s + n
+        qfull = torch.zeros(T, q.shape[1], q.shape[2])
+        qfull[s:] = q
+        outs.append(P.causal_attention(qfull, k, v, window=window)[s:])
+    return torch.cat(outs)
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+@pytest.mark.parametrize("nq,nkv,d,window", [(6, 3, 48, 0), (4, 4, 16, 0), (8, 2, 128, 0), (5, 1, 112, 0),
+                                            (2, 1, 256, 0), (6, 2, 32, 24), (4, 2, 64, 130)])
+def test_attention_generic(dtype, nq, nkv, d, window):
+    from lumenllm_b200.ops import kernels as K
+    lens, starts = [70, 1, 1, 130], [0, 299, 63, 5]
+    table, kc, vc, ks, vs, qs = _attn_case(lens, starts, nq, nkv, d, dtype, window, 5)
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(I32)
+    seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).to(I32)
+    out = K.attn_generic(dev(torch.cat(qs).to(dtype)), dev(kc.to(dtype)), dev(vc.to(dtype)), dev(table),
+                         dev(seq), dev(pos), window, d ** -0.5).cpu().float()
+    ref = _attn_ref(qs, ks, vs, lens, starts, window, dtype)
+    tol = 1e-5 if dtype == F32 else 2 ** -7
+    assert float((out - ref).abs().max()) < tol
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_attention_one_far_key_and_the_windows_edge(dtype):
+    """One key among 700 is made to dominate: the output must be its value. With a window,
+    a dominating key one place outside the window must be invisible, one place inside must
+    win."""
+    from lumenllm_b200.ops import kernels as K
+    nq, nkv, d, T = 2, 1, 32, 700
+    for window, far, expect_far in ((0, 3, True), (100, T - 100, True), (100, T - 101, False)):
+        g = gen(7)
+        k = 0.1 * torch.randn(T, nkv, d, generator=g)
+        v = torch.randn(T, nkv, d, generator=g)
+        q = 0.1 * torch.randn(1, nq, d, generator=g)
+        q[0, :, 0] = 12.0
+        k[far, 0, 0] = 12.0                                  # score 144 / sqrt(32) = 25 above the rest
+        pages = list(range(1, 12))
+        table = torch.tensor([pages], dtype=I32)
+        kc = torch.zeros(13, nkv, 64, d); vc = torch.zeros_like(kc)
+        for p in range(11):
+            n = min(64, T - 64 * p)
+            kc[pages[p], :, :n] = k[64 * p:64 * p + n].transpose(0, 1)
+            vc[pages[p], :, :n] = v[64 * p:64 * p + n].transpose(0, 1)
+        out = K.attn_generic(dev(q.to(dtype)), dev(kc.to(dtype)), dev(vc.to(dtype)), dev(table),
+                             dev(torch.zeros(1, dtype=I32)), dev(torch.tensor([T - 1], dtype=I32)),
+                             window, d ** -0.5).cpu().float()
+        target = v[far, 0].to(dtype).float()
+        close = float((out[0, 0] - target).abs().max()) < 2e-2
+        assert close == expect_far, (window, far)
+        qf = torch.zeros(T, nq, d); qf[-1] = q[0].to(dtype).float()
+        ref = P.causal_attention(qf, k.to(dtype).float(), v.to(dtype).float(), window=window)[-1:]
+        assert float((out - ref).abs().max()) < (1e-5 if dtype == F32 else 2 ** -7)
+
+
+@pytest.mark.parametrize("wdtype", [F32, BF16])
+@pytest.mark.parametrize("M,N,K_", [(1, 311, 80), (7, 64, 176), (65, 130, 48), (130, 17, 1000)])
+def test_gemm_f32_is_true_float32(wdtype, M, N, K_):
+    from lumenllm_b200.ops import kernels as K
+    g = gen(8)
+    a = torch.randn(M, K_, generator=g)
+    w = torch.randn(N, K_, generator=g).to(wdtype)
+    out = K.gemm_f32(dev(a), dev(w)).cpu()
+    ref = (a.double() @ w.double().T)
+    # float32 products summed in float32: error grows like sqrt(K) * 2^-24, far below TF32's 2^-11
+    assert float(((out.double() - ref).abs() / (1 + ref.abs())).max()) < 2e-6 * math.sqrt(K_)
+    # a row's result does not depend on the other rows of the batch
+    one = K.gemm_f32(dev(a[M // 2:M // 2 + 1].contiguous()), dev(w)).cpu()
+    assert torch.equal(one[0], out[M // 2])
+
+
+def test_argmax_ties_and_odd_vocab():
+    from lumenllm_b200.ops import kernels as K
+    V = 151936 + 7
+    lg = torch.randn(5, V, generator=gen(9))
+    lg[0, 100] = lg[0, 77777] = 50.0            # equal maxima: lowest index
+    lg[1, V - 1] = 60.0
+    lg[2, 0] = 60.0
+    lg[3] = -1.0
+    lg[4, 5] = float("nan"); lg[4, 9] = 70.0
+    out = K.argmax(dev(lg)).cpu().tolist()
+    assert out == [100, V - 1, 0, 0, 9]
+    view = dev(torch.cat([lg, lg], dim=1))[:, :V]            # rows with a stride
+    assert K.argmax(view).cpu().tolist() == out
+
+
+def _sample_rows(lg, opts, ks):
+    from lumenllm_b200.ops import kernels as K
+    o = torch.tensor(opts, dtype=F32)
+    k = torch.tensor(ks, dtype=I32)
+    return K.sample(dev(lg), dev(o), dev(k)).cpu().tolist()
+
+
+def _acceptable(row, temperature, top_k, top_p, min_p, u, tol=3e-5):
+    """Tokens the plain sampler gives for u and for u moved by a rounding's worth."""
+    return {P.sample(row, temperature, top_k, top_p, min_p, min(max(x, 0.0), 0.9999999))[0]
+            for x in (u, u - tol, u + tol)}
+
+
+@pytest.mark.parametrize("V", [1000, 50257 + 3])
+def test_sampler_against_the_plain_one(V):
+    g = gen(10)
+    settings = [(0.8, 0, 1.0, 0.0), (1.0, 50, 1.0, 0.0), (0.7, 0, 0.9, 0.0), (1.3, 0, 1.0, 0.05),
+                (1.0, 40, 0.95, 0.02), (0.0, 0, 1.0, 0.0), (0.9, 1, 0.5, 0.0), (2.0, 5, 0.5, 0.3)]
+    us = [0.0, 0.013, 0.37, 0.5, 0.77, 0.93, 0.999]
+    lg = torch.randn(len(settings) * len(us), V, generator=g) * 3
+    lg[:, 11] = lg[:, 500]                                   # equal logits inside the row
+    opts, ks = [], []
+    for (t, k, p, m) in settings:
+        for u in us:
+            opts.append([t, p, m, u]); ks.append(k)
+    got = _sample_rows(lg, opts, ks)
+    for r, (tok, o, k) in enumerate(zip(got, opts, ks)):
+        ok = _acceptable(lg[r], o[0], k, o[1], o[2], o[3])
+        assert tok in ok, (r, o, k, tok, ok)
+    # the same rows in another order and alone give the same tokens
+    perm = torch.randperm(lg.shape[0], generator=g)
+    again = _sample_rows(lg[perm], [opts[i] for i in perm], [ks[i] for i in perm])
+    assert again == [got[i] for i in perm]
+    assert _sample_rows(lg[3:4], opts[3:4], ks[3:4]) == got[3:4]
+
+
+def test_sampler_edges():
+    V = 777
+    lg = torch.full((6, V), -5.0)
+    lg[0, 3] = lg[0, 700] = 9.0                              # two equal candidates: u picks by index order
+    lg[1, :] = float("-inf"); lg[1, 42] = 0.0                 # a single finite logit
+    lg[2, :] = float("nan")                                   # nothing finite
+    lg[3, 5] = float("inf"); lg[3, 6] = 1.0                   # +inf is left out of sampling
+    lg[4, 10] = 100.0                                         # everything else underflows
+    lg[5, 1] = 2.0; lg[5, 2] = 2.0; lg[5, 3] = 2.0            # top_k cuts among equal logits
+    opts = [[1.0, 1.0, 0.0, 0.75], [1.0, 1.0, 0.0, 0.5], [1.0, 1.0, 0.0, 0.5], [1.0, 1.0, 0.0, 0.0],
+            [0.01, 1.0, 0.0, 0.99], [1.0, 1.0, 0.0, 0.99]]
+    got = _sample_rows(lg, opts, [2, 0, 0, 0, 0, 2])
+    assert got[0] == 700 and got[1] == 42 and got[2] == 0 and got[4] == 10
+    assert got[3] == 6
+    assert got[5] == 2                                        # of 1,2,3 the first two are kept
+    lo = _sample_rows(lg[:1], [[1.0, 1.0, 0.0, 0.25]], [2])
+    assert lo == [3]
