@@ -1,0 +1,271 @@
+#!/usr/bin/env python3
+"""Benchmark of lumenllm_b200 on one B200: decode tokens per second of a
+Qwen3-8B-shaped model (random bfloat16 weights, synthetic token ids) at batch 8,
+with prefill of 2,048 tokens, batch-1 and batch-64 decode, an end-to-end number
+through the Python entry point, and the HBM roofline of the decode step.
+
+    python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+
+One JSON line goes to standard output. More than one GPU is not built: the
+program says so and exits with 2.
+"""
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+# BASELINE.json configs[2]: the Qwen3-8B shape.
+SHAPE = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36,
+             hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
+             intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
+             max_position_embeddings=40960, tie_word_embeddings=False)
+CONTEXT = 4096
+PROMPT_LO, PROMPT_HI = 1024, 2048
+PREFILL_TOKENS = 2048
+
+
+def peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        d = json.load(open(path))
+        return {"hbm_gbs": float(d["hbm_gbs"]), "bf16_tflops": float(d["bf16_tflops"]),
+                "bf16_tflops_sustained": float(d.get("bf16_tflops_sustained", d["bf16_tflops"])),
+                "source": "measured"}
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0,
+            "source": "fallback"}
+
+
+class Clocks:
+    """Samples nvidia-smi while a timed region runs."""
+    Q = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self):
+        self.samples, self.proc = [], None
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", "-i", "0", f"--query-gpu={self.Q}",
+                                          "--format=csv,noheader,nounits", "-lms", "100"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.samples.append((time.perf_counter(), line.strip()))
+
+    def mark(self):
+        return time.perf_counter()
+
+    def stop(self):
+        if self.proc is not None:
+            self.proc.terminate()
+
+    def summary(self, windows):
+        sm, mx, reasons = [], 0, set()
+        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
+        for t, line in self.samples:
+            if not any(a <= t <= b for a, b in windows):
+                continue
+            f = [x.strip() for x in line.split(",")]
+            try:
+                sm.append(float(f[0])); mx = max(mx, float(f[1]))
+            except (ValueError, IndexError):
+                continue
+            for nm, v in zip(names, f[2:6]):
+                if v.lower().startswith("active"):
+                    reasons.add(nm)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": mx or None,
+                "reasons": sorted(reasons), "samples": len(sm)}
+
+
+def model_numbers(cfg, layers):
+    H, I, V = cfg["hidden_size"], cfg["intermediate_size"], cfg["vocab_size"]
+    qw = cfg["num_attention_heads"] * cfg["head_dim"]
+    kvw = cfg["num_key_value_heads"] * cfg["head_dim"]
+    per_layer = H * (qw + 2 * kvw) + qw * H + 3 * H * I
+    return {"layer_params": per_layer * layers, "head_params": V * H,
+            "kv_bytes_per_token": 2 * layers * kvw * 2}
+
+
+def decode_run(eng, B, steps, warmup, seed):
+    """Prefills B prompts (lengths uniform in [PROMPT_LO, PROMPT_HI]), then decodes greedily
+    with the sampled tokens fed back on the device. Returns per-step ms and bytes read."""
+    import torch
+    from lumenllm_b200 import StepEntry
+    from lumenllm_b200.sampling import SamplingConfig
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(PROMPT_LO, PROMPT_HI + 1, (B,), generator=g).tolist()
+    prompts = [torch.randint(0, eng.vocab_size, (n,), generator=g).tolist() for n in lens]
+    slots = [eng.alloc_slot() for _ in range(B)]
+    logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
+    cfgs = [SamplingConfig()] * B
+    tok = eng.sampler.pick(logits, cfgs, [0.0] * B)
+    entries = [(s, [0]) for s in slots]
+    for _ in range(warmup):
+        tok = eng.run_device(entries, cfgs, [0.0] * B, tokens_on_device=tok)
+    torch.cuda.synchronize()
+    ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    t0 = time.perf_counter()
+    ev0.record()
+    for _ in range(steps):
+        tok = eng.run_device(entries, cfgs, [0.0] * B, tokens_on_device=tok)
+    ev1.record()
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    ms = ev0.elapsed_time(ev1) / steps
+    mean_len = sum(lens) / B + warmup + steps / 2
+    launches = getattr(eng.graphs, "last", None)
+    per = launches.kernels_per_replay if launches is not None else 0
+    for s in slots:
+        eng.free_slot(s)
+    return {"ms": ms, "mean_len": mean_len, "window": (t0, t1), "kernels_per_step": per,
+            "tok_s": B * 1000.0 / ms}
+
+
+def prefill_run(eng, warmup, runs=5):
+    import torch
+    from lumenllm_b200 import StepEntry
+    g = torch.Generator().manual_seed(7)
+    prompt = torch.randint(0, eng.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
+    times, windows = [], []
+    for it in range(warmup + runs):
+        s = eng.alloc_slot()
+        torch.cuda.synchronize()
+        ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        t0 = time.perf_counter()
+        ev0.record()
+        eng.step([StepEntry(s, prompt, [PREFILL_TOKENS - 1])])
+        ev1.record()
+        torch.cuda.synchronize()
+        t1 = time.perf_counter()
+        eng.free_slot(s)
+        if it >= warmup:
+            times.append(ev0.elapsed_time(ev1))
+            windows.append((t0, t1))
+    return statistics.median(times), windows
+
+
+def e2e_run(built, B, steps, seed):
+    """The same decode through the public entry point: host token lists in, host token
+    lists out, one host<->device round trip per step."""
+    import torch
+    from lumenllm_b200 import GenerateRequest
+    g = torch.Generator().manual_seed(seed)
+    lens = torch.randint(PROMPT_LO, PROMPT_HI + 1, (B,), generator=g).tolist()
+    prompts = [torch.randint(0, built.engine.vocab_size, (n,), generator=g).tolist() for n in lens]
+    reqs = [GenerateRequest(p, steps + 1) for p in prompts]
+    built.generate(reqs[:1], eos_token_ids=[]) if False else None
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    outs = built.generate(reqs, eos_token_ids=[], max_batch=B)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    decode_s = max(o.decode_s for o in outs)
+    n = sum(o.completion_tokens for o in outs) - B
+    return {"tok_s": n / decode_s, "decode_s": decode_s, "window": (t0, t1)}
+
+
+def main() -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=128)
+    ap.add_argument("--warmup", type=int, default=8)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"],
+                    help="fewer layers than the shape has, for small memory (named in config)")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    args = ap.parse_args()
+    if args.impl == "reference":
+        print(json.dumps({"impl": "reference", "unavailable":
+                          "the reference is Rust + NVRTC CUDA for SM120; no Rust toolchain on "
+                          "this image, so it cannot be built or installed offline"}))
+        return 0
+    if args.gpus != 1:
+        print("bench.py: lumenllm_b200 is a single-GPU library; --gpus > 1 is not built")
+        return 2
+    warmup = max(3, args.warmup)
+    steps = max(1, args.steps)
+
+    import torch
+    from lumenllm_b200.engine import BuiltEngine, Engine
+    from lumenllm_b200.config import SamplingDefaults
+    from lumenllm_b200.ops import native
+    pk = peaks()
+    cfg = dict(SHAPE, num_hidden_layers=args.layers)
+    B = args.batch
+    top_b = B if args.no_points else max(B, 64)
+    max_tokens = max(B * CONTEXT, top_b * (PROMPT_HI + 64 + warmup + steps + 64))
+    eng = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=max_tokens,
+                             max_slots=max(top_b, 8), context_size=CONTEXT)
+    eng.graphs.min_width = CONTEXT // 64
+    built = BuiltEngine(eng, SamplingDefaults(), B)
+    nums = model_numbers(cfg, args.layers)
+    clocks = Clocks()
+    clocks.start()
+
+    launches0 = native.launches
+    main_run = decode_run(eng, B, steps, warmup, seed=1)
+    eager_launches = native.launches - launches0
+    ms = main_run["ms"]
+    weight_bytes = 2 * (nums["layer_params"] + nums["head_params"])
+    kv_bytes = B * main_run["mean_len"] * nums["kv_bytes_per_token"]
+    achieved = (weight_bytes + kv_bytes) / (ms * 1e-3) / 1e9
+
+    pre_ms, pre_windows = prefill_run(eng, warmup=3)
+    T = PREFILL_TOKENS
+    flops = 2 * T * nums["layer_params"] + 2 * nums["head_params"] \
+        + args.layers * 2 * T * T * cfg["head_dim"] * cfg["num_attention_heads"]
+    pre_frac = flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
+
+    e2e = e2e_run(built, B, min(steps, 64), seed=2)
+    points, windows = {}, [main_run["window"], e2e["window"]] + pre_windows
+    if not args.no_points:
+        for b in (1, 64):
+            r = decode_run(eng, b, min(steps, 32), warmup, seed=10 + b)
+            points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            windows.append(r["window"])
+    time.sleep(0.3)
+    clocks.stop()
+    meta_bytes = 4 * (9 * 4 * ((B + 3) // 4 + 1) + B * (CONTEXT // 64))
+    out = {
+        "metric": "decode_tokens_per_s", "value": round(main_run["tok_s"], 1), "unit": "tokens/s",
+        "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
+        "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
+        "data": "synthetic", "impl": "ours",
+        "config": {"model": "qwen3-8b-shape", "layers": args.layers,
+                   "layers_of_shape": SHAPE["num_hidden_layers"], "hidden": cfg["hidden_size"],
+                   "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
+                   "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"],
+                   "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False, "global_batch": B,
+                   "seq_len": CONTEXT, "prompt_len": f"{PROMPT_LO}..{PROMPT_HI}",
+                   "parallelism": "single", "weights": "random N(0,0.02)", "cache_page": 64,
+                   "l2": "inputs_larger_than_l2", "peaks": pk["source"]},
+        "clocks": clocks.summary(windows),
+        "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s",
+                "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * B},
+        "gpu_launches": int(main_run["kernels_per_step"] * steps) or int(eager_launches),
+        "prefill": {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
+                    "frac": round(pre_frac, 4)},
+        "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
+                     "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
+        "points": points,
+    }
+    print(json.dumps(out))
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -93,10 +93,31 @@ class EntryView:
         return self.ctx.cache.state.of(self.entry)
 
 
-def build_context(cache, runtime, entries, meta_dev=None, pad_to: int = 0, table_width: int = 0):
-    """Reserves cache room and puts the step's metadata on the device. With
-    pad_to > len(entries), padding sequences of one token are appended; they
-    write to the reserved page 0 and are read by nobody."""
+@dataclass
+class StepLayout:
+    """Where each array of a step lies in the one int32 buffer that carries them."""
+    B: int
+    N: int
+    W: int
+    width: int
+    n_groups: int
+    offs: List[int]
+    total: int
+
+    @classmethod
+    def of(cls, B, N, W, width, n_groups) -> "StepLayout":
+        sizes = [N, N, N, N, B, B, B, B + 1, W] + [B * width] * n_groups
+        offs = [0]
+        for s in sizes:
+            offs.append(offs[-1] + _pad4(s))
+        return cls(B, N, W, width, n_groups, offs, offs[-1])
+
+
+def pack_step(cache, entries, pad_to: int = 0, table_width: int = 0, want_padding: bool = False):
+    """Reserves cache room for the entries and lays the step's metadata out on the host.
+    With pad_to > len(entries), padding sequences of one token are appended: they write
+    to the reserved page 0 and are read by nobody (with want_padding their logits are
+    computed too, so that a captured step keeps its shapes)."""
     starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
     B_real = len(entries)
     B = max(B_real, pad_to)
@@ -104,14 +125,13 @@ def build_context(cache, runtime, entries, meta_dev=None, pad_to: int = 0, table
     starts_all = starts + [0] * (B - B_real)
     slots = [e.slot for e in entries] + [-1] * (B - B_real)
     N = sum(q_lens)
-    W = sum(len(e.want) for e in entries)
+    W = sum(len(e.want) for e in entries) + ((B - B_real) if want_padding else 0)
     n_groups = len(cache.groups)
     width = max(pages_for(s + q) for s, q in zip(starts_all, q_lens))
     width = max(width, table_width, 1)
-    sizes = [N, N, N, N, B, B, B, B + 1, W] + [B * width] * n_groups
-    offs = np.cumsum([0] + [_pad4(s) for s in sizes])
-    total = int(offs[-1])
-    host = np.zeros((total,), dtype=np.int32)
+    lay = StepLayout.of(B, N, W, width, n_groups)
+    offs = lay.offs
+    host = np.zeros((lay.total,), dtype=np.int32)
     tok = host[offs[0]:offs[0] + N]
     rpos = host[offs[1]:offs[1] + N]
     cpos = host[offs[2]:offs[2] + N]
@@ -126,6 +146,9 @@ def build_context(cache, runtime, entries, meta_dev=None, pad_to: int = 0, table
             for x in entries[b].want:
                 want[w] = n + int(x)
                 w += 1
+        elif want_padding:
+            want[w] = n
+            w += 1
         pos = np.arange(starts_all[b], starts_all[b] + q, dtype=np.int32)
         rpos[n:n + q] = pos
         cpos[n:n + q] = pos
@@ -138,21 +161,38 @@ def build_context(cache, runtime, entries, meta_dev=None, pad_to: int = 0, table
     host[offs[6]:offs[6] + B] = q_lens
     for gi, g in enumerate(cache.groups):
         bt = host[offs[9 + gi]:offs[9 + gi] + B * width].reshape(B, width)
+        wcols = min(width, g.table.shape[1])
         for b in range(B_real):
-            wcols = min(width, g.table.shape[1])
             bt[b, :wcols] = g.table[slots[b], :wcols]
-    if meta_dev is None or total > meta_dev.numel():
-        grow = max(total, 2 * (0 if meta_dev is None else meta_dev.numel()), 1 << 14)
-        meta_dev = torch.empty((grow,), dtype=torch.int32, device=runtime.device)
-    pinned = torch.from_numpy(host).pin_memory()
-    dev = meta_dev[:total]
-    dev.copy_(pinned, non_blocking=True)
-    sl = lambda i, n_: dev[int(offs[i]):int(offs[i]) + n_]
+    return host, lay, q_lens, starts_all, slots, B_real
+
+
+def context_on(dev: torch.Tensor, lay: StepLayout, q_lens, starts, slots, n_real, cache, runtime):
+    """A StepContext whose arrays are views of `dev`, laid out as `lay` says."""
+    offs = lay.offs
+    sl = lambda i, n_: dev[offs[i]:offs[i] + n_]
+    B, N = lay.B, lay.N
     return StepContext(
-        runtime=runtime, B=B, N=N, q_lens=q_lens, starts=starts_all, slots=slots,
+        runtime=runtime, B=B, N=N, q_lens=list(q_lens), starts=list(starts), slots=list(slots),
         tokens=sl(0, N), rope_pos=sl(1, N), cache_pos=sl(2, N), tok_seq=sl(3, N),
         seq_slot=sl(4, B), seq_start=sl(5, B), seq_qlen=sl(6, B), cu_q=sl(7, B + 1),
-        want_rows=sl(8, W),
-        block_tables=[sl(9 + gi, B * width).view(B, width) for gi in range(n_groups)],
-        cache=cache, n_real=B_real), meta_dev
+        want_rows=sl(8, lay.W),
+        block_tables=[sl(9 + gi, B * lay.width).view(B, lay.width) for gi in range(lay.n_groups)],
+        cache=cache, n_real=n_real)
 
+
+def upload(host: np.ndarray, dev: torch.Tensor) -> None:
+    """One asynchronous copy from pinned memory; the pinned block is not used again
+    before the copy has run (the host allocator waits for it)."""
+    dev[:host.size].copy_(torch.from_numpy(host).pin_memory(), non_blocking=True)
+
+
+def build_context(cache, runtime, entries, meta_dev=None, pad_to: int = 0, table_width: int = 0):
+    """pack_step + upload + context_on; returns the context and the (possibly regrown)
+    device buffer."""
+    host, lay, q_lens, starts, slots, n_real = pack_step(cache, entries, pad_to, table_width)
+    if meta_dev is None or lay.total > meta_dev.numel():
+        grow = max(lay.total, 2 * (0 if meta_dev is None else meta_dev.numel()), 1 << 14)
+        meta_dev = torch.empty((grow,), dtype=torch.int32, device=runtime.device)
+    upload(host, meta_dev)
+    return context_on(meta_dev[:lay.total], lay, q_lens, starts, slots, n_real, cache, runtime), meta_dev

@@ -44,7 +44,8 @@ def require_gpu(device=None) -> torch.device:
 class Engine:
     def __init__(self, spec: ModelSpec, weights: Dict[str, torch.Tensor], dtype="bfloat16",
                  max_tokens: int = 8192, max_slots: Optional[int] = None, device=None,
-                 config=None, context_size: Optional[int] = None, max_step_tokens: int = 8192):
+                 config=None, context_size: Optional[int] = None, max_step_tokens: int = 8192,
+                 use_graphs: bool = True):
         if dtype not in _DTYPES:
             raise ConfigError(f"dtype {dtype!r}: bfloat16 or float32")
         self.device = require_gpu(device)
@@ -66,6 +67,9 @@ class Engine:
         self.sampler = DeviceSampler(self.device)
         self._meta_dev = torch.empty((1 << 16,), dtype=torch.int32, device=self.device)
         self.steps_run = 0
+        from .decode_graph import DecodeGraphs
+        self.graphs = DecodeGraphs(self)
+        self.use_graphs = bool(use_graphs)
 
     # ------------------------------------------------------------ construction
     @classmethod
@@ -206,8 +210,21 @@ class Engine:
     def run(self, entries, configs, uniforms) -> List[int]:
         """Backend face of the generation loop: feeds each (slot, tokens), samples one
         token per sequence from the logits at its last token, returns them on the host."""
+        return self.run_device(entries, configs, uniforms).tolist()
+
+    def run_device(self, entries, configs, uniforms, tokens_on_device=None) -> torch.Tensor:
+        """As `run`, but the sampled tokens stay on the device (int32 [len(entries)])."""
+        if self.use_graphs and self.model.graph_safe and all(len(t) == 1 for _, t in entries):
+            self._validate([StepEntry(s, t, [0]) for s, t in entries])
+            try:
+                return self.graphs.step(entries, configs, uniforms, tokens_on_device)
+            except CacheFull as e:
+                raise StepError(str(e)) from e
+        if tokens_on_device is not None:
+            toks = tokens_on_device.tolist()
+            entries = [(s, [toks[i]]) for i, (s, _) in enumerate(entries)]
         logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in entries])
-        return self.sampler.pick(logits, configs, uniforms).tolist()
+        return self.sampler.pick(logits, configs, uniforms)
 
     def generate(self, requests, eos_token_ids=None, max_batch: int = 64, on_token=None):
         """`requests`: one GenerateRequest or a list. Returns GenerateOutput(s)."""

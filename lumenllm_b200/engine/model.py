@@ -35,6 +35,10 @@ class DecoderModel:
         self.final_norm = build_part("norm", spec.final_norm, weights, runtime)
         self.head = build_part("head", spec.head, weights, runtime)
         self.schedule = spec.schedule
+        # a step can be captured in a CUDA graph only if no part looks at the step's
+        # host-side lists; parts say so with `graph_safe = True`
+        self.graph_safe = all(getattr(b.mixer, "graph_safe", False) and
+                              getattr(b.ffn, "graph_safe", False) for b in self.blocks)
 
     # what the cache must hold, per schedule entry
     def cache_needs(self) -> Dict[int, CacheNeed]:

@@ -61,8 +61,13 @@ def fn(module: str, name: str, argtypes):
     return f
 
 
+launches = 0   # kernels of this library launched (or recorded into a graph) so far
+
+
 def check(code: int, what: str) -> None:
+    global launches
     if code == 0:
+        launches += 1
         return
     if code == ERR_UNSUPPORTED:
         raise KernelError(f"{what}: this kernel does not take these sizes")

@@ -21,6 +21,8 @@ from .linear import Linear
 
 @register_part("mixer", "gqa_attention")
 class GQAttention:
+    graph_safe = True
+
     @classmethod
     def tensors(cls, spec):
         p = spec.params

@@ -13,6 +13,8 @@ from .linear import Linear
 
 @register_part("ffn", "swiglu")
 class SwiGLU:
+    graph_safe = True
+
     @classmethod
     def tensors(cls, spec):
         H = int(need(spec.params, "hidden_size", "swiglu"))
