@@ -27,6 +27,25 @@ import torch
 from .slots import CacheError, CacheFull, PagePool, SlotAllocator
 
 PAGE = 64
+LAYOUT_LINEAR, LAYOUT_SW128 = 0, 1
+
+
+def tile_layout(dtype, head_dim: int) -> int:
+    """How a (page, kv head) tile is laid out: bfloat16 tiles whose head size is a
+    multiple of 64 are kept in the 128-byte-swizzled form that the tensor-core kernels
+    stage with plain bulk copies; everything else is [key][head_dim]."""
+    return LAYOUT_SW128 if (dtype == torch.bfloat16 and head_dim % 64 == 0) else LAYOUT_LINEAR
+
+
+def _aligned_zeros(shape, dtype, device, align=1024):
+    """Zeros whose first byte lies on an `align`-byte boundary (tiles must)."""
+    n = 1
+    for s in shape:
+        n *= s
+    item = torch.empty((), dtype=dtype).element_size()
+    raw = torch.zeros((n * item + align,), dtype=torch.uint8, device=device)
+    off = (-raw.data_ptr()) % align
+    return raw[off:off + n * item].view(dtype).view(shape)
 
 
 @dataclass(frozen=True)
@@ -50,9 +69,10 @@ class CacheGroup:
         self.pool = PagePool(n_pages, reserved=1)
         total = n_pages + 1
         shape = (len(self.entries), total, need.n_kv, PAGE, need.head_dim)
+        self.layout = tile_layout(dtype, need.head_dim)
         if device is not None:
-            self.k = torch.zeros(shape, dtype=dtype, device=device)
-            self.v = torch.zeros(shape, dtype=dtype, device=device)
+            self.k = _aligned_zeros(shape, dtype, device)
+            self.v = _aligned_zeros(shape, dtype, device)
         else:  # bookkeeping only (host tests)
             self.k = self.v = None
         self.table = np.zeros((max_slots, max_pages_per_seq), dtype=np.int32)

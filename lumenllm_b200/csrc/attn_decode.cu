@@ -1,0 +1,275 @@
+// Decode attention over the paged cache for bfloat16, split over the keys.
+//
+// One query token per sequence. A block takes one chunk of 128 keys (two pages) of
+// one kv head of one sequence and serves all query heads of that kv head at once,
+// so every key and value is read from HBM exactly once per step. The two K tiles and
+// two V tiles of the chunk are staged by four bulk asynchronous copies
+// (cp.async.bulk, completion on an mbarrier): a page tile is contiguous and already
+// in the 128-byte-swizzled layout, so no tensor map and no address arithmetic per
+// element is needed. Each of the four warps then owns 32 keys: S = Q K^T and
+// O = P V run on the tensor cores (mma.sync m16n8k16, the query heads of the group
+// padded to 16 rows; the kernel is bound by HBM, the padding costs nothing), softmax
+// in float32. The block merges its four warps and writes one partial (unnormalised
+// O, running max m, sum l) per (sequence, head, chunk); a second kernel merges the
+// chunks in rising order. Chunk edges are multiples of 128 in absolute position, so
+// the result for a token does not depend on its neighbours in the batch.
+//
+// Scratch: part_o [B, nq, max_chunks, D] and part_ml [B, nq, max_chunks, 2] float32.
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+#define AD_THREADS 128
+#define AD_CHUNK 128
+
+template <int D>
+__global__ void __launch_bounds__(AD_THREADS)
+attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
+                   const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
+                   int bt_stride, const int* __restrict__ seq_pos, float* __restrict__ part_o,
+                   float* __restrict__ part_ml, int nq, int nkv, int window, float scale,
+                   int max_chunks, int* __restrict__ err) {
+    constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;
+    extern __shared__ __align__(1024) unsigned char smem[];
+    unsigned char* Ks = smem;                    // 2 tiles
+    unsigned char* Vs = smem + 2 * TILE_BYTES;   // 2 tiles
+    __shared__ uint64_t bars[2];
+    __shared__ float s_m[4][16], s_l[4][16];
+
+    const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int p = seq_pos[b];
+    int lo = 0;
+    if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
+    if (c < lo / AD_CHUNK || c > p / AD_CHUNK) return;
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int G = nq / nkv;
+
+    if (tid == 0) {
+        mbar_init(&bars[0], 1);
+        mbar_init(&bars[1], 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    if (tid == 0) {
+        const int* bt = block_table + (size_t)b * bt_stride;
+        const int pg0 = bt[2 * c];
+        const int pg1 = (2 * c + 1 < bt_stride) ? bt[2 * c + 1] : 0;
+        const size_t t0 = ((size_t)pg0 * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+        const size_t t1 = ((size_t)pg1 * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+        mbar_expect_tx(&bars[0], 2 * TILE_BYTES);
+        bulk_load(Ks, kcache + t0, TILE_BYTES, &bars[0]);
+        bulk_load(Ks + TILE_BYTES, kcache + t1, TILE_BYTES, &bars[0]);
+        mbar_expect_tx(&bars[1], 2 * TILE_BYTES);
+        bulk_load(Vs, vcache + t0, TILE_BYTES, &bars[1]);
+        bulk_load(Vs + TILE_BYTES, vcache + t1, TILE_BYTES, &bars[1]);
+    }
+
+    // Query fragments: rows = the G heads of this kv head (zero beyond G).
+    uint32_t qa[D / 16][4];
+    {
+        const __nv_bfloat16* q0 = q + ((size_t)b * nq + (size_t)kvh * G + g) * D;
+        const __nv_bfloat16* q1 = q0 + (size_t)8 * D;
+        const bool r0 = g < G, r1 = g + 8 < G;
+#pragma unroll
+        for (int ks = 0; ks < D / 16; ++ks) {
+            const int col = 16 * ks + 2 * t;
+            qa[ks][0] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + col) : 0u;
+            qa[ks][1] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + col) : 0u;
+            qa[ks][2] = r0 ? *reinterpret_cast<const uint32_t*>(q0 + col + 8) : 0u;
+            qa[ks][3] = r1 ? *reinterpret_cast<const uint32_t*>(q1 + col + 8) : 0u;
+        }
+    }
+
+    const bool k_ok = mbar_wait(&bars[0], 0);
+    const uint32_t ktile = smem_u32(Ks) + (warp >> 1) * TILE_BYTES;
+    const uint32_t vtile = smem_u32(Vs) + (warp >> 1) * TILE_BYTES;
+    const int rb = (warp & 1) * 32;
+
+    // S = Q K^T for this warp's 32 keys.
+    float s[4][4];
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
+#pragma unroll
+        for (int kp = 0; kp < D / 32; ++kp) {
+            uint32_t r[4];
+            const int row = rb + 8 * nt + (lane & 7);
+            ldsm_x4(r, ktile + sw_off(row, 4 * kp + (lane >> 3)));
+            mma_bf16(s[nt], qa[2 * kp], r[0], r[1]);
+            mma_bf16(s[nt], qa[2 * kp + 1], r[2], r[3]);
+        }
+    }
+    // Mask, scale, softmax pieces of this warp (rows g and g + 8).
+    const int jbase = c * AD_CHUNK + warp * 32;
+    float m0 = -INFINITY, m1 = -INFINITY;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            const int j = jbase + 8 * nt + 2 * t + i;
+            const bool valid = (j >= lo) && (j <= p);
+            s[nt][i] = valid ? s[nt][i] * scale : -INFINITY;
+            s[nt][2 + i] = valid ? s[nt][2 + i] * scale : -INFINITY;
+            m0 = fmaxf(m0, s[nt][i]);
+            m1 = fmaxf(m1, s[nt][2 + i]);
+        }
+    }
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
+    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
+    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
+    const float ms0 = (m0 == -INFINITY) ? 0.0f : m0, ms1 = (m1 == -INFINITY) ? 0.0f : m1;
+    float l0 = 0.0f, l1 = 0.0f;
+#pragma unroll
+    for (int nt = 0; nt < 4; ++nt) {
+#pragma unroll
+        for (int i = 0; i < 2; ++i) {
+            s[nt][i] = expf(s[nt][i] - ms0);
+            s[nt][2 + i] = expf(s[nt][2 + i] - ms1);
+            l0 += s[nt][i];
+            l1 += s[nt][2 + i];
+        }
+    }
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
+    uint32_t pa[2][4];
+#pragma unroll
+    for (int kk = 0; kk < 2; ++kk) {
+        pa[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
+        pa[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
+        pa[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
+        pa[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
+    }
+
+    // O = P V.
+    const bool v_ok = mbar_wait(&bars[1], 0);
+    float o[D / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.0f;
+#pragma unroll
+    for (int dtp = 0; dtp < D / 16; ++dtp) {
+#pragma unroll
+        for (int kk = 0; kk < 2; ++kk) {
+            uint32_t r[4];
+            const int mi = lane >> 3;
+            const int row = rb + 16 * kk + (mi & 1) * 8 + (lane & 7);
+            ldsm_x4_t(r, vtile + sw_off(row, 2 * dtp + (mi >> 1)));
+            mma_bf16(o[2 * dtp], pa[kk], r[0], r[1]);
+            mma_bf16(o[2 * dtp + 1], pa[kk], r[2], r[3]);
+        }
+    }
+    // One decision for the whole block (it is also the barrier before the K tiles are reused).
+    if (__syncthreads_or(!(k_ok && v_ok))) {
+        if (tid == 0) atomicExch(err, 1);
+        // a second bounded wait for the copies still in flight, then leave
+        mbar_wait(&bars[0], 0);
+        mbar_wait(&bars[1], 0);
+        return;
+    }
+
+    // Merge the four warps through shared memory (the K tiles are no longer read).
+    float* so = reinterpret_cast<float*>(Ks);   // [4][G][D]
+    if (t == 0) {
+        if (g < G) { s_m[warp][g] = m0; s_l[warp][g] = l0; }
+        if (g + 8 < G) { s_m[warp][g + 8] = m1; s_l[warp][g + 8] = l1; }
+    }
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt) {
+        if (g < G) {
+            float* dst = so + ((size_t)(warp * G + g)) * D + 8 * dt + 2 * t;
+            dst[0] = o[dt][0];
+            dst[1] = o[dt][1];
+        }
+        if (g + 8 < G) {
+            float* dst = so + ((size_t)(warp * G + g + 8)) * D + 8 * dt + 2 * t;
+            dst[0] = o[dt][2];
+            dst[1] = o[dt][3];
+        }
+    }
+    __syncthreads();
+    for (int idx = tid; idx < G * D; idx += AD_THREADS) {
+        const int row = idx / D, e = idx - row * D;
+        float M = fmaxf(fmaxf(s_m[0][row], s_m[1][row]), fmaxf(s_m[2][row], s_m[3][row]));
+        float acc = 0.0f, l = 0.0f;
+#pragma unroll
+        for (int w = 0; w < 4; ++w) {
+            const float mw = s_m[w][row];
+            const float f = (mw == -INFINITY) ? 0.0f : expf(mw - M);
+            acc += so[((size_t)(w * G + row)) * D + e] * f;
+            l += s_l[w][row] * f;
+        }
+        const size_t pi = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks + c;
+        part_o[pi * D + e] = acc;
+        if (e == 0) {
+            part_ml[pi * 2] = M;
+            part_ml[pi * 2 + 1] = l;
+        }
+    }
+}
+
+// Merges the chunks of one (sequence, head) in rising order.
+template <typename TOut>
+__global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
+                                           const float* __restrict__ part_ml,
+                                           const int* __restrict__ seq_pos, TOut* __restrict__ out,
+                                           int nq, int D, int window, int max_chunks) {
+    const int head = blockIdx.x, b = blockIdx.y;
+    const int p = seq_pos[b];
+    int lo = 0;
+    if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
+    const int c0 = lo / AD_CHUNK, c1 = p / AD_CHUNK;
+    const size_t base = ((size_t)b * nq + head) * max_chunks;
+    float M = -INFINITY;
+    for (int c = c0; c <= c1; ++c) M = fmaxf(M, part_ml[(base + c) * 2]);
+    float L = 0.0f;
+    for (int c = c0; c <= c1; ++c) L += part_ml[(base + c) * 2 + 1] * expf(part_ml[(base + c) * 2] - M);
+    const float inv = 1.0f / L;
+    for (int e = threadIdx.x; e < D; e += blockDim.x) {
+        float acc = 0.0f;
+        for (int c = c0; c <= c1; ++c)
+            acc += part_o[(base + c) * D + e] * expf(part_ml[(base + c) * 2] - M);
+        out[((size_t)b * nq + head) * D + e] = from_f32<TOut>(acc * inv);
+    }
+}
+
+// Entry point. q, out: bfloat16 [B, nq, D]; caches in the swizzled layout; seq_pos[b] is the
+// position of sequence b's query (its cached length before this token). part_o and part_ml are
+// the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
+LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* vcache,
+                                const int* block_table, int bt_stride, const int* seq_pos,
+                                void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
+                                int d, int window, float scale, int max_chunks, int* err,
+                                cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || max_chunks <= 0)
+        return LUMEN_ERR_UNSUPPORTED;
+    if (B > 65535 || nkv > 65535) return LUMEN_ERR_UNSUPPORTED;
+    if (2 * max_chunks > bt_stride + 1) return LUMEN_ERR_BAD_ARGUMENT;
+    dim3 grid(max_chunks, nkv, B);
+    const __nv_bfloat16* qp = (const __nv_bfloat16*)q;
+    const __nv_bfloat16* kp = (const __nv_bfloat16*)kcache;
+    const __nv_bfloat16* vp = (const __nv_bfloat16*)vcache;
+    if (d == 128) {
+        const int smem = 4 * LUMEN_PAGE * 128 * 2;
+        auto k = attn_decode_kernel<128>;
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        k<<<grid, AD_THREADS, smem, stream>>>(qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
+                                              nq, nkv, window, scale, max_chunks, err);
+    } else if (d == 64) {
+        const int smem = 4 * LUMEN_PAGE * 64 * 2;
+        auto k = attn_decode_kernel<64>;
+        k<<<grid, AD_THREADS, smem, stream>>>(qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
+                                              nq, nkv, window, scale, max_chunks, err);
+    } else {
+        return LUMEN_ERR_UNSUPPORTED;
+    }
+    LUMEN_LAUNCH_CHECK();
+    dim3 cgrid(nq, B);
+    attn_decode_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, stream>>>(
+        part_o, part_ml, seq_pos, (__nv_bfloat16*)out, nq, d, window, max_chunks);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}

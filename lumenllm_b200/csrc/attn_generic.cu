@@ -19,7 +19,8 @@ __global__ void __launch_bounds__(AG_THREADS)
 attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const T* __restrict__ vcache,
                     const int* __restrict__ block_table, int bt_stride,
                     const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
-                    T* __restrict__ out, int nq, int nkv, int d, int window, float scale) {
+                    T* __restrict__ out, int nq, int nkv, int d, int window, float scale,
+                    int layout) {
     __shared__ float qs[AG_MAX_D];
     __shared__ float ps[AG_THREADS];
     __shared__ float red[32];
@@ -42,9 +43,10 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
         float s = -INFINITY;
         if (valid) {
             const int page = bt[j / LUMEN_PAGE];
-            const T* krow = kcache + (((size_t)page * nkv + kvh) * LUMEN_PAGE + (j % LUMEN_PAGE)) * d;
+            const T* ktile = kcache + ((size_t)page * nkv + kvh) * LUMEN_PAGE * d;
+            const int r = j % LUMEN_PAGE;
             float dot = 0.0f;
-            for (int e = 0; e < d; ++e) dot = fmaf(qs[e], to_f32(krow[e]), dot);
+            for (int e = 0; e < d; ++e) dot = fmaf(qs[e], to_f32(ktile[tile_offset(layout, r, e, d)]), dot);
             s = dot * scale;
         }
         const float cm = block_max(s, red);
@@ -61,10 +63,12 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
         const int jbeg = max(c * AG_THREADS, lo), jend = min(c * AG_THREADS + AG_THREADS - 1, p);
         for (int jj = jbeg; jj <= jend; ++jj) {
             const int page = bt[jj / LUMEN_PAGE];
-            const T* vrow = vcache + (((size_t)page * nkv + kvh) * LUMEN_PAGE + (jj % LUMEN_PAGE)) * d;
+            const T* vtile = vcache + ((size_t)page * nkv + kvh) * LUMEN_PAGE * d;
+            const int r = jj % LUMEN_PAGE;
             const float w = ps[jj - c * AG_THREADS];
-            if (tid < d) acc0 = fmaf(w, to_f32(vrow[tid]), acc0);
-            if (tid + AG_THREADS < d) acc1 = fmaf(w, to_f32(vrow[tid + AG_THREADS]), acc1);
+            if (tid < d) acc0 = fmaf(w, to_f32(vtile[tile_offset(layout, r, tid, d)]), acc0);
+            if (tid + AG_THREADS < d)
+                acc1 = fmaf(w, to_f32(vtile[tile_offset(layout, r, tid + AG_THREADS, d)]), acc1);
         }
         m = m_new;
         __syncthreads();
@@ -78,20 +82,22 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
 LUMEN_API int lumen_attn_generic(const void* q, const void* kcache, const void* vcache,
                                  const int* block_table, int bt_stride, const int* tok_seq,
                                  const int* tok_pos, void* out, int is_bf16, int N, int nq, int nkv,
-                                 int d, int window, float scale, cudaStream_t stream) {
+                                 int d, int window, float scale, int layout, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (d <= 0 || d > AG_MAX_D || nq <= 0 || nkv <= 0 || nq % nkv != 0 || window < 0)
         return LUMEN_ERR_UNSUPPORTED;
     if (nq > 65535) return LUMEN_ERR_UNSUPPORTED;
+    if (layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64 != 0)) return LUMEN_ERR_UNSUPPORTED;
     dim3 grid(N, nq);
     if (is_bf16)
         attn_generic_kernel<__nv_bfloat16><<<grid, AG_THREADS, 0, stream>>>(
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
-            block_table, bt_stride, tok_seq, tok_pos, (__nv_bfloat16*)out, nq, nkv, d, window, scale);
+            block_table, bt_stride, tok_seq, tok_pos, (__nv_bfloat16*)out, nq, nkv, d, window, scale,
+            layout);
     else
         attn_generic_kernel<float><<<grid, AG_THREADS, 0, stream>>>(
             (const float*)q, (const float*)kcache, (const float*)vcache, block_table, bt_stride,
-            tok_seq, tok_pos, (float*)out, nq, nkv, d, window, scale);
+            tok_seq, tok_pos, (float*)out, nq, nkv, d, window, scale, layout);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -19,6 +19,25 @@
 // for values), so one (page, kv head) tile is contiguous.
 #define LUMEN_PAGE 64
 
+// Layouts of a (page, kv head) tile of the cache, LUMEN_PAGE keys x d values.
+//   LUMEN_LAYOUT_LINEAR: [key][d].
+//   LUMEN_LAYOUT_SW128 (2-byte elements, d a multiple of 64): [d/64][key][64], every
+//     row 128 bytes, and the 16-byte chunk c of row `key` stored at chunk c ^ (key & 7).
+//     This is the 128-byte-swizzled K-major tile that ldmatrix reads without bank
+//     conflicts and that a tensor-core descriptor (SWIZZLE_128B) addresses directly, so
+//     a plain bulk copy of the tile is all a kernel needs to stage it.
+#define LUMEN_LAYOUT_LINEAR 0
+#define LUMEN_LAYOUT_SW128 1
+
+// Offset, in elements, of value e of key r inside its tile.
+__host__ __device__ __forceinline__ int tile_offset(int layout, int r, int e, int d) {
+    if (layout == LUMEN_LAYOUT_SW128) {
+        const int cb = e >> 6, ce = e & 63;
+        return cb * (LUMEN_PAGE * 64) + r * 64 + ((((ce >> 3) ^ (r & 7)) << 3) | (ce & 7));
+    }
+    return r * d + e;
+}
+
 #define LUMEN_LAUNCH_CHECK()                         \
     do {                                             \
         cudaError_t e__ = cudaGetLastError();        \

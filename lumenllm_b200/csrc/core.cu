@@ -135,7 +135,7 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const f
                                           const int* __restrict__ tok_seq,
                                           const int* __restrict__ block_table, int bt_stride,
                                           T* __restrict__ q_out, T* __restrict__ kcache,
-                                          T* __restrict__ vcache, int nq, int nkv, int d) {
+                                          T* __restrict__ vcache, int nq, int nkv, int d, int layout) {
     extern __shared__ float rowbuf[];  // [warps][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x;
@@ -170,17 +170,17 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const f
         }
         __syncwarp();
     }
-    T* dst;
     if (is_q) {
-        dst = q_out + ((size_t)n * nq + head) * d;
+        T* dst = q_out + ((size_t)n * nq + head) * d;
+        for (int e = lane; e < d; e += 32) dst[e] = from_f32<T>(x[e]);
     } else {
         const int kvh = is_k ? head - nq : head - nq - nkv;
         const int cp = cache_pos[n];
         const int page = block_table[(size_t)tok_seq[n] * bt_stride + cp / LUMEN_PAGE];
-        const size_t off = (((size_t)page * nkv + kvh) * LUMEN_PAGE + (cp % LUMEN_PAGE)) * d;
-        dst = (is_k ? kcache : vcache) + off;
+        T* tile = (is_k ? kcache : vcache) + ((size_t)page * nkv + kvh) * LUMEN_PAGE * d;
+        const int r = cp % LUMEN_PAGE;
+        for (int e = lane; e < d; e += 32) tile[tile_offset(layout, r, e, d)] = from_f32<T>(x[e]);
     }
-    for (int e = lane; e < d; e += 32) dst[e] = from_f32<T>(x[e]);
 }
 
 LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, const float* qw, const float* kw, float eps,
@@ -188,10 +188,12 @@ LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, const float* qw, const 
                                        const int* cache_pos, const int* tok_seq,
                                        const int* block_table, int bt_stride, void* q_out,
                                        void* kcache, void* vcache, int is_bf16, int N, int nq,
-                                       int nkv, int d, cudaStream_t stream) {
+                                       int nkv, int d, int layout, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (d <= 0 || d > QKR_MAX_D || (d & 1) || rot < 0 || rot > d || (rot & 1) || nq < 0 || nkv < 0)
         return LUMEN_ERR_UNSUPPORTED;
+    if (layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64 != 0)) return LUMEN_ERR_UNSUPPORTED;
+    if (layout != LUMEN_LAYOUT_SW128 && layout != LUMEN_LAYOUT_LINEAR) return LUMEN_ERR_BAD_ARGUMENT;
     const int warps = 4;
     const int nheads = nq + 2 * nkv;
     if (nheads == 0) return 0;
@@ -200,11 +202,11 @@ LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, const float* qw, const 
     if (is_bf16)
         qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
             qkv, qw, kw, eps, inv_freq, rot, rope_pos, cache_pos, tok_seq, block_table, bt_stride,
-            (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nq, nkv, d);
+            (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nq, nkv, d, layout);
     else
         qk_norm_rope_store_kernel<float><<<grid, warps * 32, smem, stream>>>(
             qkv, qw, kw, eps, inv_freq, rot, rope_pos, cache_pos, tok_seq, block_table, bt_stride,
-            (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, d);
+            (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, d, layout);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -87,6 +87,11 @@ class EntryView:
         k, v, g = self.ctx.cache.entry_storage(self.cache_entry)
         return k, v, self.ctx.block_tables[g]
 
+    @property
+    def layout(self) -> int:
+        """Tile layout of this run's cache pages (cache.kv.LAYOUT_*)."""
+        return self.ctx.cache.groups[self.ctx.cache.group_of[self.cache_entry]].layout
+
     def state(self):
         """Per-sequence state of fixed size: [max_slots, *shape]; row seq_slot[b] belongs
         to sequence b. None if the mixer declared none."""

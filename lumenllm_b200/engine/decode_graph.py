@@ -13,6 +13,8 @@ cuda/runtime/graph.rs:8-32).
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, List, Sequence, Tuple
 
 import numpy as np
@@ -44,9 +46,19 @@ class _Captured:
 
 class DecodeGraphs:
     def __init__(self, engine):
-        self.engine = engine
+        # no strong reference back to the engine: an engine that is dropped must free its
+        # graphs at once, not whenever the cycle collector runs (which may be in the middle
+        # of another engine's capture, where destroying a graph is not permitted)
+        self._engine = weakref.ref(engine)
         self.captured: Dict[Tuple[int, int, bool], _Captured] = {}
         self.min_width = 1      # page-table width to capture for at least (saves re-captures)
+
+    @property
+    def engine(self):
+        eng = self._engine()
+        if eng is None:
+            raise RuntimeError("the engine of these graphs is gone")
+        return eng
 
     def _capture(self, key, lay: StepLayout, host, lists) -> _Captured:
         eng = self.engine
@@ -79,8 +91,15 @@ class DecodeGraphs:
         from ..ops import native
         graph = torch.cuda.CUDAGraph()
         before = native.launches
-        with torch.cuda.graph(graph):
-            logits = body()
+        gc.collect()
+        was_enabled = gc.isenabled()
+        gc.disable()          # no finaliser may touch CUDA while the stream is capturing
+        try:
+            with torch.cuda.graph(graph):
+                logits = body()
+        finally:
+            if was_enabled:
+                gc.enable()
         cap = _Captured(graph, meta, opts, top_k, logits, next_tok, ctx)
         cap.kernels_per_replay = native.launches - before
         return cap

@@ -16,6 +16,7 @@ BF16 = torch.bfloat16
 I32 = torch.int32
 
 PAGE = 64  # tokens per cache page; equals LUMEN_PAGE in csrc/common.cuh
+LAYOUT_LINEAR, LAYOUT_SW128 = 0, 1   # tile layouts of the cache, as in csrc/common.cuh
 
 
 def _is_bf16(t) -> int:
@@ -81,7 +82,8 @@ def silu_mul(gu, out_dtype):
 
 
 def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, rope_pos, cache_pos,
-                       tok_seq, block_table, kcache, vcache, nq, nkv, d, out_dtype):
+                       tok_seq, block_table, kcache, vcache, nq, nkv, d, out_dtype,
+                       layout=LAYOUT_LINEAR):
     """Per-head RMSNorm of q and k, rotation, q out and k/v written to the paged cache.
     qkv float32 [N, (nq + 2 nkv) d]; caches [pages, nkv, PAGE, d] of out_dtype
     (None with nkv == 0: a layer that reads another layer's cache)."""
@@ -108,15 +110,18 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, rope_
         require(kcache, out_dtype, "kcache")
         require(vcache, out_dtype, "vcache")
     f = fn("core", "lumen_qk_norm_rope_store",
-           [P, P, P, c_float, P, c_int, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, P])
+           [P, P, P, c_float, P, c_int, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int,
+            c_int, P])
     check(f(ptr(qkv), ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(inv_freq), int(rotary_dim),
             ptr(rope_pos), ptr(cache_pos), ptr(tok_seq), ptr(block_table), block_table.stride(0),
-            ptr(q_out), ptr(kcache), ptr(vcache), _is_bf16(q_out), N, nq, nkv, d, stream_ptr()),
+            ptr(q_out), ptr(kcache), ptr(vcache), _is_bf16(q_out), N, nq, nkv, d, int(layout),
+            stream_ptr()),
           "qk_norm_rope_store")
     return q_out
 
 
-def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale):
+def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale,
+                 layout=LAYOUT_LINEAR):
     """Causal attention of N query tokens over the paged cache. q [N, nq, d]."""
     N, nq, d = q.shape
     nkv = kcache.shape[1]
@@ -130,9 +135,9 @@ def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale
         raise KernelError(f"attention takes head sizes in steps of 16 up to 256, not {d}")
     out = torch.empty_like(q)
     f = fn("attn_generic", "lumen_attn_generic",
-           [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, P])
+           [P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(tok_seq),
-            ptr(tok_pos), ptr(out), _is_bf16(q), N, nq, nkv, d, int(window), float(scale),
+            ptr(tok_pos), ptr(out), _is_bf16(q), N, nq, nkv, d, int(window), float(scale), int(layout),
             stream_ptr()), "attn_generic")
     return out
 
@@ -179,4 +184,77 @@ def sample(logits, opts, top_k, out=None):
     f = fn("sample", "lumen_sample", [P, c_longlong, c_int, c_int, P, P, P, P])
     check(f(ptr(logits), logits.stride(0), B, V, ptr(opts), ptr(top_k), ptr(out), stream_ptr()),
           "sample")
+    return out
+
+
+_err_flags = {}
+
+
+def error_flag(device) -> torch.Tensor:
+    """A device int that kernels with bounded waits set when a wait ran out."""
+    key = torch.device(device).index
+    t = _err_flags.get(key)
+    if t is None:
+        t = _err_flags[key] = torch.zeros((1,), dtype=I32, device=device)
+    return t
+
+
+def check_error_flags() -> None:
+    """Raises if any kernel gave up on a wait since the last check (synchronises)."""
+    for dev, t in _err_flags.items():
+        if int(t.item()) != 0:
+            t.zero_()
+            raise KernelError(f"a kernel on cuda:{dev} gave up waiting for its own copies")
+
+
+def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
+    """Split-KV decode attention, bfloat16, swizzled cache, head size 64 or 128, at most
+    16 query heads per kv head. q [B, nq, d]; seq_pos int32 [B]: each query's position."""
+    B, nq, d = q.shape
+    nkv = kcache.shape[1]
+    require(q, BF16, "attn_decode.q")
+    require(kcache, BF16, "attn_decode.kcache")
+    require(vcache, BF16, "attn_decode.vcache")
+    require(block_table, I32, "attn_decode.block_table")
+    require(seq_pos, I32, "attn_decode.seq_pos")
+    if seq_pos.numel() < B or block_table.shape[0] < B:
+        raise KernelError("attn_decode: metadata shorter than the batch")
+    width = block_table.shape[1]
+    max_chunks = (width + 1) // 2
+    out = torch.empty_like(q)
+    part_o = torch.empty((B, nq, max_chunks, d), dtype=F32, device=q.device)
+    part_ml = torch.empty((B, nq, max_chunks, 2), dtype=F32, device=q.device)
+    f = fn("attn_decode", "lumen_attn_decode",
+           [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P])
+    check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(seq_pos),
+            ptr(out), ptr(part_o), ptr(part_ml), B, nq, nkv, d, int(window), float(scale), max_chunks,
+            ptr(error_flag(q.device)), stream_ptr()), "attn_decode")
+    return out
+
+
+def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window, scale):
+    """Causal flash attention for sequences that bring q_lens[b] tokens each (host list),
+    bfloat16, swizzled cache, head size 64 or 128, at most 16 query heads per kv head.
+    q [N, nq, d]; cu_q int32 [B+1]; seq_start int32 [B]."""
+    N, nq, d = q.shape
+    nkv = kcache.shape[1]
+    B = len(q_lens)
+    require(q, BF16, "attn_prefill.q")
+    require(kcache, BF16, "attn_prefill.kcache")
+    require(vcache, BF16, "attn_prefill.vcache")
+    require(block_table, I32, "attn_prefill.block_table")
+    require(cu_q, I32, "attn_prefill.cu_q")
+    require(seq_start, I32, "attn_prefill.seq_start")
+    if nq % nkv or nq // nkv > 16:
+        raise KernelError("attn_prefill: at most 16 query heads per kv head")
+    if cu_q.numel() < B + 1 or seq_start.numel() < B or block_table.shape[0] < B or sum(q_lens) != N:
+        raise KernelError("attn_prefill: metadata does not match the batch")
+    tq = 64 // (nq // nkv)
+    n_tiles = sum((n + tq - 1) // tq for n in q_lens)
+    out = torch.empty_like(q)
+    f = fn("attn_prefill", "lumen_attn_prefill",
+           [P, P, P, P, c_int, P, P, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P, P])
+    check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(cu_q),
+            ptr(seq_start), B, n_tiles, ptr(out), nq, nkv, d, int(window), float(scale),
+            ptr(error_flag(q.device)), stream_ptr()), "attn_prefill")
     return out

@@ -86,9 +86,20 @@ class GQAttention:
                                  self.position.inv_freq, self.position.rotary_dim,
                                  ctx.rope_pos, ctx.cache_pos, ctx.tok_seq, table,
                                  kc if nkv_new else None, vc if nkv_new else None,
-                                 self.nq, nkv_new, self.d, self.runtime.dtype)
-        out = self.attend(q, kc, vc, table, ctx)
+                                 self.nq, nkv_new, self.d, self.runtime.dtype, layout=entry.layout)
+        out = self.attend(q, kc, vc, table, ctx, entry.layout)
         return self.o(out.view(-1, self.nq * self.d), split_ok=True)
 
-    def attend(self, q, kc, vc, table, ctx):
-        return K.attn_generic(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale)
+    def attend(self, q, kc, vc, table, ctx, layout):
+        """Chooses the kernel by the step's shape: the split-KV kernel when every sequence
+        brings one token, the flash kernel for prompts, and the general kernel for the
+        32-bit path and for head sizes the fast kernels do not take. All agree within rounding."""
+        fast = (layout == K.LAYOUT_SW128 and q.dtype == torch.bfloat16 and self.d in (64, 128)
+                and self.nq // self.nkv <= 16)
+        if fast and ctx.is_decode:
+            return K.attn_decode(q, kc, vc, table, ctx.cache_pos, self.window, self.scale)
+        if fast:
+            return K.attn_prefill(q, kc, vc, table, ctx.cu_q, ctx.seq_start, ctx.q_lens, self.window,
+                                  self.scale)
+        return K.attn_generic(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale,
+                              layout=layout)

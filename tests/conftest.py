@@ -23,11 +23,13 @@ def pytest_collection_modifyitems(config, items):
             item.add_marker(skip)
 
 
-# Three tiny configurations of the architecture that differ in every size and option:
+# Tiny configurations of the architecture that differ in every size and option:
 # layers, width, heads, groups (ratio 2 / 4 / 1), head size (16 / 32 / 48, so heads x size is
 # equal to, larger than and different from the width), feed-forward width, vocabulary (a power
 # of two, a multiple of 128, a prime), theta, eps, tied or untied head, and window (none, none,
-# 24 keys on the layers from index 1 on).
+# 24 keys on the layers from index 1 on). D and E have the head sizes (64, 128) that the
+# tensor-core attention kernels take, with groups of 2 and 4 and, for D, a window of 40 keys on
+# its second layer, so that the engine's tests run through those kernels too.
 TINY = {
     "A": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=64,
               num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=16,
@@ -44,6 +46,16 @@ TINY = {
               intermediate_size=176, vocab_size=311, rope_theta=50000.0, rms_norm_eps=3e-6,
               max_position_embeddings=1536, tie_word_embeddings=False, attention_bias=False,
               use_sliding_window=True, sliding_window=24, max_window_layers=1, hidden_act="silu"),
+    "D": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=128,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=64,
+              intermediate_size=192, vocab_size=500, rope_theta=100000.0, rms_norm_eps=1e-6,
+              max_position_embeddings=1024, tie_word_embeddings=False, attention_bias=False,
+              use_sliding_window=True, sliding_window=40, max_window_layers=1, hidden_act="silu"),
+    "E": dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", hidden_size=128,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=1, head_dim=128,
+              intermediate_size=160, vocab_size=272, rope_theta=1000000.0, rms_norm_eps=1e-5,
+              max_position_embeddings=1024, tie_word_embeddings=True, attention_bias=False,
+              use_sliding_window=False, hidden_act="silu"),
 }
 
 

@@ -19,7 +19,7 @@ from conftest import ROOT, TINY, seeded_tokens, tolerance
 pytestmark = pytest.mark.gpu
 
 DTYPES = ["float32", "bfloat16"]
-NAMES = ["A", "B", "C"]
+NAMES = ["A", "B", "C", "D", "E"]
 
 
 @pytest.fixture(scope="module")
@@ -134,7 +134,7 @@ def test_slots_and_pages_used_again_hold_no_stale_keys(dtype, plain, tiny_models
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("name", ["A", "C"])
+@pytest.mark.parametrize("name", ["A", "C", "D", "E"])
 def test_long_decoding(name, dtype, plain, engines):
     """3 prompt tokens, then 400 single tokens: page edges, the 128-key chunk edges of the
     attention kernels, and for C the window sliding over page edges."""

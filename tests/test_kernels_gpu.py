@@ -70,15 +70,19 @@ def test_silu_mul(out_dtype):
     assert float(((z - ref).abs() / (1 + ref.abs())).max()) < tol
 
 
-def _paged(T, nkv, d, dtype, n_pages, seed):
-    """A page table that walks the pool backwards with a gap, so that position order and
-    page order differ."""
-    need = (T + 63) // 64
-    pages = list(range(n_pages - 1, 0, -2))[:need]
-    assert len(pages) == need
-    k = torch.zeros(n_pages, nkv, 64, d, dtype=dtype)
-    v = torch.zeros(n_pages, nkv, 64, d, dtype=dtype)
-    return pages, k, v
+def to_sw128(x):
+    """[..., 64, d] tiles in key-major order -> the same tiles in the swizzled layout:
+    [d/64][key][64] with the 16-byte chunk c of row `key` at chunk c ^ (key & 7)."""
+    *lead, R, d = x.shape
+    x = x.reshape(*lead, R, d // 64, 8, 8)
+    r = torch.arange(R)
+    phys = (torch.arange(8)[None, :] ^ (r[:, None] & 7))                 # [R, 8]
+    idx = phys[:, None, :, None].expand(R, d // 64, 8, 8)
+    idx = idx.expand(*lead, R, d // 64, 8, 8) if lead else idx
+    out = torch.empty_like(x).scatter_(-2, idx.contiguous(), x)
+    nd = out.dim()
+    out = out.permute(*range(nd - 4), nd - 3, nd - 4, nd - 2, nd - 1)     # [..., cb, R, 8, 8]
+    return out.reshape(*lead, R, d)                                       # same bytes, new order
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
@@ -209,6 +213,104 @@ def test_attention_one_far_key_and_the_windows_edge(dtype):
         qf = torch.zeros(T, nq, d); qf[-1] = q[0].to(dtype).float()
         ref = P.causal_attention(qf, k.to(dtype).float(), v.to(dtype).float(), window=window)[-1:]
         assert float((out - ref).abs().max()) < (1e-5 if dtype == F32 else 2 ** -7)
+
+
+def test_swizzled_writer_and_reader_agree():
+    """The cache writer in the swizzled layout, read back by the general kernel and compared
+    with the same data in the plain layout."""
+    from lumenllm_b200.ops import kernels as K
+    nq, nkv, d = 4, 2, 128
+    g = gen(11)
+    N = 150
+    qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g)
+    pos = torch.arange(N, dtype=I32)
+    seq = torch.zeros(N, dtype=I32)
+    table = torch.tensor([[5, 2, 7]], dtype=I32)
+    outs, caches = [], []
+    for layout in (K.LAYOUT_LINEAR, K.LAYOUT_SW128):
+        kc = torch.zeros(9, nkv, 64, d, dtype=BF16).cuda()
+        vc = torch.zeros_like(kc)
+        q = K.qk_norm_rope_store(dev(qkv), None, None, 0.0, None, 0, dev(pos), dev(pos), dev(seq),
+                                 dev(table), kc, vc, nq, nkv, d, BF16, layout=layout)
+        outs.append(K.attn_generic(q, kc, vc, dev(table), dev(seq), dev(pos), 0, d ** -0.5,
+                                   layout=layout).cpu())
+        caches.append((kc.cpu(), vc.cpu()))
+    assert torch.equal(outs[0], outs[1])
+    assert torch.equal(to_sw128(caches[0][0]), caches[1][0])
+    assert torch.equal(to_sw128(caches[0][1]), caches[1][1])
+
+
+@pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, 0), (4, 2, 64, 0), (32, 8, 128, 0), (3, 1, 64, 0),
+                                            (16, 1, 128, 0), (4, 4, 64, 0), (8, 2, 128, 100), (4, 2, 64, 130)])
+def test_attention_decode_kernel(nq, nkv, d, window):
+    """Split-KV decode attention: lengths 1, 64, 128, 129, 300 and 1000 keys in one batch."""
+    from lumenllm_b200.ops import kernels as K
+    starts = [0, 63, 127, 128, 299, 999]
+    lens = [1] * len(starts)
+    table, kc, vc, ks, vs, qs = _attn_case(lens, starts, nq, nkv, d, BF16, window, 12, n_pages=60)
+    pos = torch.tensor(starts, dtype=I32)
+    out = K.attn_decode(dev(torch.cat(qs).to(BF16)), dev(to_sw128(kc.to(BF16))), dev(to_sw128(vc.to(BF16))),
+                        dev(table), dev(pos), window, d ** -0.5).cpu().float()
+    K.check_error_flags()
+    ref = _attn_ref(qs, ks, vs, lens, starts, window, BF16)
+    assert float((out - ref).abs().max()) < 2 ** -6
+    # a wider page table (as a captured step has) changes nothing
+    wide = torch.zeros(table.shape[0], 32, dtype=I32); wide[:, :table.shape[1]] = table
+    out2 = K.attn_decode(dev(torch.cat(qs).to(BF16)), dev(to_sw128(kc.to(BF16))), dev(to_sw128(vc.to(BF16))),
+                         dev(wide), dev(pos), window, d ** -0.5).cpu().float()
+    assert torch.equal(out, out2)
+
+
+@pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, 0), (4, 2, 64, 0), (6, 2, 64, 0), (5, 1, 128, 0),
+                                            (16, 1, 64, 0), (2, 2, 128, 0), (8, 2, 128, 70), (4, 2, 64, 24)])
+def test_attention_prefill_kernel(nq, nkv, d, window):
+    """Flash attention for prompts: whole prompts, continuations from a cached prefix, and
+    single tokens, of unequal lengths in one batch."""
+    from lumenllm_b200.ops import kernels as K
+    lens, starts = [70, 1, 1, 130, 17, 200], [0, 299, 63, 5, 64, 0]
+    table, kc, vc, ks, vs, qs = _attn_case(lens, starts, nq, nkv, d, BF16, window, 13, n_pages=60)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=I32)
+    out = K.attn_prefill(dev(torch.cat(qs).to(BF16)), dev(to_sw128(kc.to(BF16))), dev(to_sw128(vc.to(BF16))),
+                         dev(table), dev(cu), dev(torch.tensor(starts, dtype=I32)), lens, window,
+                         d ** -0.5).cpu().float()
+    K.check_error_flags()
+    ref = _attn_ref(qs, ks, vs, lens, starts, window, BF16)
+    err = (out - ref).abs().max(dim=-1).values.max(dim=-1).values
+    assert float(err.max()) < 2 ** -6, (int(err.argmax()), float(err.max()))
+
+
+@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+def test_fast_attention_one_far_key_and_the_windows_edge(kernel):
+    from lumenllm_b200.ops import kernels as K
+    nq, nkv, d, T = 4, 1, 128, 700
+    for window, far, expect_far in ((0, 3, True), (100, T - 100, True), (100, T - 101, False)):
+        g = gen(7)
+        k = 0.1 * torch.randn(T, nkv, d, generator=g)
+        v = torch.randn(T, nkv, d, generator=g)
+        q = 0.1 * torch.randn(1, nq, d, generator=g)
+        q[0, :, 0] = 12.0
+        k[far, 0, 0] = 12.0
+        pages = list(range(11, 0, -1))
+        table = torch.tensor([pages], dtype=I32)
+        kc = torch.zeros(13, nkv, 64, d); vc = torch.zeros_like(kc)
+        for p in range(11):
+            n = min(64, T - 64 * p)
+            kc[pages[p], :, :n] = k[64 * p:64 * p + n].transpose(0, 1)
+            vc[pages[p], :, :n] = v[64 * p:64 * p + n].transpose(0, 1)
+        args = (dev(q.to(BF16)), dev(to_sw128(kc.to(BF16))), dev(to_sw128(vc.to(BF16))), dev(table))
+        if kernel == "decode":
+            out = K.attn_decode(*args, dev(torch.tensor([T - 1], dtype=I32)), window, d ** -0.5)
+        else:
+            out = K.attn_prefill(*args, dev(torch.tensor([0, 1], dtype=I32)),
+                                 dev(torch.tensor([T - 1], dtype=I32)), [1], window, d ** -0.5)
+        out = out.cpu().float()
+        K.check_error_flags()
+        target = v[far, 0].to(BF16).float()
+        close = float((out[0, 0] - target).abs().max()) < 2e-2
+        assert close == expect_far, (window, far)
+        qf = torch.zeros(T, nq, d); qf[-1] = q[0].to(BF16).float()
+        ref = P.causal_attention(qf, k.to(BF16).float(), v.to(BF16).float(), window=window)[-1:]
+        assert float((out - ref).abs().max()) < 2 ** -6
 
 
 @pytest.mark.parametrize("wdtype", [F32, BF16])
