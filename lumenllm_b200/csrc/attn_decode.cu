@@ -273,3 +273,64 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
+
+// ---------------------------------------------------------------------------------------
+// The same decode attention for callers that must not allocate (declared and described in
+// attn_decode_noalloc.h; the reference has no counterpart). The partial results live in one
+// fixed array that is part of this library's device image.
+// ---------------------------------------------------------------------------------------
+#include <cstdio>
+#include <mutex>
+
+#include "attn_decode_noalloc.h"
+
+static __device__ __align__(256) float lumen_decode_scratch[LUMEN_DECODE_NOALLOC_MAX_FLOATS];
+
+#define LUMEN_NOALLOC_MAX_DEVICES 64
+// Device address of lumen_decode_scratch on each device, looked up once per device. In host
+// code the array's NAME is only a handle of the runtime, not memory a kernel may touch; the
+// address a kernel needs comes from cudaGetSymbolAddress with that device current.
+static float* s_scratch_on_device[LUMEN_NOALLOC_MAX_DEVICES];
+static std::mutex s_scratch_lock;
+
+LUMEN_API int lumen_attn_decode_noalloc(const void* q, const void* kcache, const void* vcache,
+                                        const int* block_table, int bt_stride, const int* seq_pos,
+                                        void* out, int B, int nq, int nkv, int d, int window,
+                                        float scale, int max_chunks, int* err, cudaStream_t stream) {
+    if (B <= 0) return 0;
+    if (nq <= 0 || max_chunks <= 0 || d <= 0) return LUMEN_ERR_UNSUPPORTED;
+    const unsigned long long rows = (unsigned long long)B * (unsigned long long)nq *
+                                    (unsigned long long)max_chunks;
+    const unsigned long long need = rows * (unsigned long long)(d + 2);
+    if (need > (unsigned long long)LUMEN_DECODE_NOALLOC_MAX_FLOATS) {
+        std::fprintf(stderr,
+                     "lumen_attn_decode_noalloc: batch %d x heads %d x chunks %d x (head size %d + 2) = "
+                     "%llu floats of scratch, the built-in array holds %llu; use a smaller batch or "
+                     "page table, or the allocating entry point lumen_attn_decode\n",
+                     B, nq, max_chunks, d, need, (unsigned long long)LUMEN_DECODE_NOALLOC_MAX_FLOATS);
+        return LUMEN_ERR_SCRATCH_TOO_SMALL;
+    }
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return (int)e;
+    if (dev < 0 || dev >= LUMEN_NOALLOC_MAX_DEVICES) return LUMEN_ERR_UNSUPPORTED;
+    float* scratch;
+    {
+        std::lock_guard<std::mutex> guard(s_scratch_lock);
+        if (s_scratch_on_device[dev] == nullptr) {
+            float* p = nullptr;
+            e = cudaGetSymbolAddress((void**)&p, lumen_decode_scratch);
+            if (e != cudaSuccess) return (int)e;
+            if (p == nullptr) return LUMEN_ERR_BAD_ARGUMENT;
+            s_scratch_on_device[dev] = p;
+        }
+        scratch = s_scratch_on_device[dev];
+    }
+    // Nothing in the scratch has to start at zero: every (sequence, head, chunk) entry that
+    // the merge kernel reads is written in full by this call's first kernel; entries of
+    // chunks outside a sequence's range keep older contents and are never read.
+    float* part_o = scratch;
+    float* part_ml = scratch + rows * (unsigned long long)d;
+    return lumen_attn_decode(q, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml,
+                             B, nq, nkv, d, window, scale, max_chunks, err, stream);
+}

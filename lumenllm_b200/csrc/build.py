@@ -30,7 +30,7 @@ MODULES = {
     "gemm_f32": (["gemm_f32.cu"], ["common.cuh"]),
     "attn_generic": (["attn_generic.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),
-    "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh"]),
+    "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "attn_decode_noalloc.h"]),
     "attn_prefill": (["attn_prefill.cu"], ["common.cuh", "mma_utils.cuh"]),
 }
 

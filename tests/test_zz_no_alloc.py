@@ -1,0 +1,97 @@
+"""The decode-attention entry point that allocates nothing, called the way a program without
+PyTorch's allocator would call it: through its exported C symbol, with raw device pointers.
+
+Such callers exist: code running inside another framework's allocator hooks, plug-ins with a
+memory budget fixed at start-up, serving loops that forbid cudaMalloc on the hot path, C or Rust
+programs that link the shared object directly. For them `lumen_attn_decode_noalloc` keeps the
+per-chunk partial results in an array that is part of the library. This test checks, on two
+calls in a row with different batches (the second meets what the first left in the array), that
+it returns what the ordinary entry point returns, and that a batch too large for the array is
+refused without a launch.
+
+The file name sorts last so that a run that stops at the first failure has already run every
+other test; it passes alone in a fresh process as well.
+"""
+import ctypes
+
+import pytest
+import torch
+
+pytestmark = pytest.mark.gpu
+
+ERR_SCRATCH_TOO_SMALL = 100004
+MAX_FLOATS = 4 * 1024 * 1024
+
+
+def _case(B, nq, nkv, d, lens, n_pages, width, seed):
+    """Random swizzled caches are as good as any: both entry points read the same bytes."""
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(B, nq, d, generator=g).to(torch.bfloat16).cuda()
+    kc = torch.randn(n_pages, nkv, 64, d, generator=g).to(torch.bfloat16).cuda()
+    vc = torch.randn(n_pages, nkv, 64, d, generator=g).to(torch.bfloat16).cuda()
+    table = torch.zeros(B, width, dtype=torch.int32)
+    free = list(range(1, n_pages))
+    for b, n in enumerate(lens):
+        for p in range((n + 63) // 64):
+            table[b, p] = free.pop()
+    pos = torch.tensor([n - 1 for n in lens], dtype=torch.int32).cuda()
+    return q, kc, vc, table.cuda(), pos
+
+
+def _noalloc_fn():
+    from lumenllm_b200.csrc import build
+    lib = ctypes.CDLL(str(build.ensure_built(["attn_decode"])["attn_decode"]))
+    f = lib.lumen_attn_decode_noalloc
+    f.restype = ctypes.c_int
+    P, I = ctypes.c_void_p, ctypes.c_int
+    f.argtypes = [P, P, P, P, I, P, P, I, I, I, I, I, ctypes.c_float, I, P, P]
+    return f
+
+
+def _call(f, q, kc, vc, table, pos, window, err):
+    B, nq, d = q.shape
+    out = torch.empty_like(q)
+    rc = f(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), table.stride(0),
+           pos.data_ptr(), out.data_ptr(), B, nq, kc.shape[1], d, window, float(d) ** -0.5,
+           (table.shape[1] + 1) // 2, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+    return rc, out
+
+
+def test_no_alloc_entry_point_matches_the_allocating_one_twice():
+    from lumenllm_b200.ops import kernels as K
+    f = _noalloc_fn()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    cases = [
+        dict(B=5, nq=8, nkv=2, d=128, lens=[1, 64, 129, 700, 1000], n_pages=48, width=16, window=0),
+        dict(B=3, nq=4, nkv=2, d=64, lens=[300, 17, 128], n_pages=20, width=8, window=100),
+    ]
+    for i, c in enumerate(cases):
+        window = c.pop("window")
+        q, kc, vc, table, pos = _case(seed=20 + i, **c)
+        expected = K.attn_decode(q, kc, vc, table, pos, window, float(q.shape[2]) ** -0.5)
+        torch.cuda.synchronize()
+        got = None                                            # drop the last call's output first
+        before = torch.cuda.memory_allocated()
+        rc, got = _call(f, q, kc, vc, table, pos, window, err)
+        grown = torch.cuda.memory_allocated() - before        # only `out` was made, by the test
+        assert 0 <= grown <= got.numel() * 2 + 512
+        assert rc == 0, f"call {i} returned {rc}"
+        torch.cuda.synchronize()
+        assert int(err.item()) == 0
+        assert torch.isfinite(got.float()).all()
+        # the tests of the allocating entry point allow 2^-6 against the plain implementation;
+        # the two entry points run the same kernels and must agree at least that well
+        assert float((got.float() - expected.float()).abs().max()) < 2 ** -6, f"call {i}"
+    K.check_error_flags()
+
+
+def test_no_alloc_entry_point_refuses_what_does_not_fit(capfd):
+    f = _noalloc_fn()
+    err = torch.zeros(1, dtype=torch.int32, device="cuda")
+    B, nq, nkv, d, width = 64, 32, 8, 128, 64
+    assert B * nq * ((width + 1) // 2) * (d + 2) > MAX_FLOATS
+    q, kc, vc, table, pos = _case(B, nq, nkv, d, [10] * B, 80, width, 30)
+    rc, out = _call(f, q, kc, vc, table, pos, 0, err)
+    assert rc == ERR_SCRATCH_TOO_SMALL
+    assert "floats of scratch" in capfd.readouterr().err
+    torch.cuda.synchronize()
