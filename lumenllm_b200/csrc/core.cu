@@ -1,25 +1,55 @@
 // Memory-bound parts of a decoder step: embedding gather, residual add + RMSNorm,
-// SiLU(gate)*up, and the fused per-head RMSNorm + rotary encoding + cache write.
-// All arithmetic is float32; the output type T is float (32-bit path) or
-// __nv_bfloat16. Compiled without fast-math: sqrtf, expf and sincosf are the
-// precise forms.
+// SiLU(gate)*up, the table of rotation angles, and the fused per-head RMSNorm + rotary
+// encoding + cache write. All arithmetic is float32; the output type T is float (32-bit
+// path) or __nv_bfloat16. Compiled without fast-math: sqrtf, expf and sincosf are the
+// precise forms. Rows whose length is a multiple of 4 move as 16-byte vectors.
+//
+// Inputs that come from a split matrix product arrive as S partial results [S, rows, width];
+// they are added in rising order of S while they are read.
 #include "common.cuh"
 
+template <typename T> struct Pack4;
+template <> struct Pack4<float> {
+    static __device__ __forceinline__ void store(float* p, float a, float b, float c, float d) {
+        *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
+    }
+};
+template <> struct Pack4<__nv_bfloat16> {
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float a, float b, float c, float d) {
+        __nv_bfloat162 lo = __floats2bfloat162_rn(a, b), hi = __floats2bfloat162_rn(c, d);
+        uint2 v;
+        v.x = *reinterpret_cast<uint32_t*>(&lo);
+        v.y = *reinterpret_cast<uint32_t*>(&hi);
+        *reinterpret_cast<uint2*>(p) = v;
+    }
+};
+__device__ __forceinline__ float4 load4(const float* p) { return *reinterpret_cast<const float4*>(p); }
+__device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
+    const uint2 v = *reinterpret_cast<const uint2*>(p);
+    const __nv_bfloat162 lo = *reinterpret_cast<const __nv_bfloat162*>(&v.x);
+    const __nv_bfloat162 hi = *reinterpret_cast<const __nv_bfloat162*>(&v.y);
+    return make_float4(__low2float(lo), __high2float(lo), __low2float(hi), __high2float(hi));
+}
+
 // ---------------------------------------------------------------- embedding
-// h[t, :] = float(E[token[t], :]); a token outside the table writes zeros (the
-// host has refused it before; this is the second guard).
+// h[t, :] = float(E[token[t], :]); a token outside the table writes zeros (the host has
+// refused it before; this is the second guard).
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ h, int H, int V) {
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* out = h + (size_t)t * H;
-    if (tok < 0 || tok >= V) {
-        for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = 0.0f;
-        return;
+    const bool ok = tok >= 0 && tok < V;
+    const TW* row = table + (size_t)(ok ? tok : 0) * H;
+    if ((H & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            const float4 v = ok ? load4(row + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+            *reinterpret_cast<float4*>(out + i) = v;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = ok ? to_f32(row[i]) : 0.0f;
     }
-    const TW* row = table + (size_t)tok * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) out[i] = to_f32(row[i]);
 }
 
 LUMEN_API int lumen_embed(const int* tokens, const void* table, int table_is_bf16, float* h,
@@ -35,32 +65,57 @@ LUMEN_API int lumen_embed(const int* tokens, const void* table, int table_is_bf1
 }
 
 // ---------------------------------------------------------------- add + RMSNorm
-// x = h[r] + delta[0][r] + ... + delta[S-1][r] (summed in that order, float32);
-// if write_h the sum is stored back to h[r]; y = x * 1/sqrt(mean(x^2)+eps) * w.
-// With `rows`, block b reads row rows[b] and writes y row b (gather of the
-// wanted rows); without, row b.
+// x = h[r] + delta[0][r] + ... + delta[S-1][r] (summed in that order, float32); if write_h the
+// sum is stored back to h[r]; y = x * 1/sqrt(mean(x^2)+eps) * w. With `rows`, block b reads
+// row rows[b] and writes y row b (gather of the wanted rows); without, row b.
 template <typename TOut>
-__global__ void add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S,
-                                   size_t delta_stride, const float* __restrict__ w, float eps,
-                                   TOut* __restrict__ y, const int* __restrict__ rows, int H,
-                                   int write_h) {
-    extern __shared__ float xs[];  // H floats
+__global__ void __launch_bounds__(256)
+add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
+                   const float* __restrict__ w, float eps, TOut* __restrict__ y,
+                   const int* __restrict__ rows, int H, int write_h) {
+    extern __shared__ __align__(16) float xs[];  // H floats
     __shared__ float red[32];
     const int b = blockIdx.x;
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
+    const float* dr = delta + (size_t)r * H;
     float ss = 0.0f;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) {
-        float x = hr[i];
-        for (int s = 0; s < S; ++s) x += delta[(size_t)s * delta_stride + (size_t)r * H + i];
-        xs[i] = x;
-        if (write_h && S > 0) hr[i] = x;
-        ss += x * x;
+    if ((H & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            float4 x = load4(hr + i);
+            for (int s = 0; s < S; ++s) {
+                const float4 d = load4(dr + (size_t)s * delta_stride + i);
+                x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+            }
+            *reinterpret_cast<float4*>(xs + i) = x;
+            if (write_h && S > 0) *reinterpret_cast<float4*>(hr + i) = x;
+            ss += x.x * x.x;
+            ss += x.y * x.y;
+            ss += x.z * x.z;
+            ss += x.w * x.w;
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) {
+            float x = hr[i];
+            for (int s = 0; s < S; ++s) x += dr[(size_t)s * delta_stride + i];
+            xs[i] = x;
+            if (write_h && S > 0) hr[i] = x;
+            ss += x * x;
+        }
     }
     ss = block_sum(ss, red);
     const float scale = 1.0f / sqrtf(ss / (float)H + eps);
     TOut* yr = y + (size_t)b * H;
-    for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<TOut>(xs[i] * scale * w[i]);
+    if ((H & 3) == 0) {
+        for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
+            const float4 x = *reinterpret_cast<const float4*>(xs + i);
+            const float4 g = load4(w + i);
+            Pack4<TOut>::store(yr + i, x.x * scale * g.x, x.y * scale * g.y, x.z * scale * g.z,
+                               x.w * scale * g.w);
+        }
+    } else {
+        for (int i = threadIdx.x; i < H; i += blockDim.x) yr[i] = from_f32<TOut>(xs[i] * scale * w[i]);
+    }
 }
 
 LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long long delta_stride,
@@ -87,56 +142,101 @@ LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long 
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// gu: [N, 2*I] float32 with the gate in columns [0, I) and up in [I, 2I).
+// gu: [S, N, 2*I] float32 partials with the gate in columns [0, I) and up in [I, 2I).
 template <typename TOut>
-__global__ void silu_mul_kernel(const float* __restrict__ gu, TOut* __restrict__ z, long long total,
-                                int I) {
+__global__ void silu_mul_kernel(const float* __restrict__ gu, int S, size_t split_stride,
+                                TOut* __restrict__ z, long long total, int I) {
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long step = (long long)gridDim.x * blockDim.x;
-    for (; idx < total; idx += step) {
-        const long long n = idx / I;
-        const int i = (int)(idx - n * I);
-        const float g = gu[n * 2 * I + i];
-        const float u = gu[n * 2 * I + I + i];
-        z[idx] = from_f32<TOut>(g / (1.0f + expf(-g)) * u);
+    if ((I & 3) == 0) {
+        const long long total4 = total >> 2;
+        const int I4 = I >> 2;
+        for (; idx < total4; idx += step) {
+            const long long n = idx / I4;
+            const int i = (int)(idx - n * I4) * 4;
+            const float* gp = gu + n * 2 * I + i;
+            float4 g = load4(gp), u = load4(gp + I);
+            for (int s = 1; s < S; ++s) {
+                const float4 g2 = load4(gp + s * split_stride), u2 = load4(gp + s * split_stride + I);
+                g.x += g2.x; g.y += g2.y; g.z += g2.z; g.w += g2.w;
+                u.x += u2.x; u.y += u2.y; u.z += u2.z; u.w += u2.w;
+            }
+            Pack4<TOut>::store(z + n * I + i, g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                               g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w);
+        }
+    } else {
+        for (; idx < total; idx += step) {
+            const long long n = idx / I;
+            const int i = (int)(idx - n * I);
+            float g = gu[n * 2 * I + i], u = gu[n * 2 * I + I + i];
+            for (int s = 1; s < S; ++s) {
+                g += gu[s * split_stride + n * 2 * I + i];
+                u += gu[s * split_stride + n * 2 * I + I + i];
+            }
+            z[idx] = from_f32<TOut>(g / (1.0f + expf(-g)) * u);
+        }
     }
 }
 
-LUMEN_API int lumen_silu_mul(const float* gu, void* z, int z_is_bf16, int N, int I,
+LUMEN_API int lumen_silu_mul(const float* gu, int n_splits, void* z, int z_is_bf16, int N, int I,
                              cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (I <= 0) return LUMEN_ERR_BAD_ARGUMENT;
+    if (I <= 0 || n_splits < 1) return LUMEN_ERR_BAD_ARGUMENT;
     const long long total = (long long)N * I;
-    long long blocks = (total + 255) / 256;
+    const size_t stride = (size_t)N * 2 * I;
+    long long blocks = (total / 4 + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
+    if (blocks < 1) blocks = 1;
     if (z_is_bf16)
-        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(gu, (__nv_bfloat16*)z, total, I);
+        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(gu, n_splits, stride,
+                                                                       (__nv_bfloat16*)z, total, I);
     else
-        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>(gu, (float*)z, total, I);
+        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>(gu, n_splits, stride, (float*)z, total, I);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// ---------------------------------------------------------------- rotation angles
+// cs[n, i] = (cos, sin) of angle = float(pos[n]) * inv_freq[i], i < half. Made once per step
+// and read by every layer that shares the position encoding.
+__global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
+                                  float2* __restrict__ cs, int N, int half) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= (long long)N * half) return;
+    const int n = (int)(idx / half), i = (int)(idx - (long long)n * half);
+    const float ang = (float)pos[n] * inv_freq[i];
+    float s, c;
+    sincosf(ang, &s, &c);
+    cs[idx] = make_float2(c, s);
+}
+
+LUMEN_API int lumen_rope_table(const int* pos, const float* inv_freq, float* cs, int N, int half,
+                               cudaStream_t stream) {
+    if (N <= 0 || half <= 0) return 0;
+    const long long total = (long long)N * half;
+    rope_table_kernel<<<(int)((total + 255) / 256), 256, 0, stream>>>(pos, inv_freq, (float2*)cs, N, half);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
 
 // ---------------------------------------------------------------- q/k norm + rotary + cache write
-// Input row n of `qkv` holds nq query heads, then nkv key heads, then nkv value
-// heads, d floats each. One warp per (token, head):
-//   q, k: optional RMSNorm over the head's d values with a weight of length d,
-//         then rotation of pairs (i, i + rot/2), i < rot/2, by
-//         angle = float(pos) * inv_freq[i];
+// Input row n of `qkv` (the sum of S partials) holds nq query heads, then nkv key heads, then
+// nkv value heads, d floats each. One warp per (token, head):
+//   q, k: optional RMSNorm over the head's d values with a weight of length d, then rotation
+//         of pairs (i, i + rot/2), i < rot/2, by the angles of cs[n];
 //   q goes to q_out[n, head, :]; k and v go to the paged cache at
 //   page = block_table[tok_seq[n], cache_pos[n] / PAGE], row cache_pos[n] % PAGE.
 #define QKR_MAX_D 512
 template <typename T>
-__global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const float* __restrict__ qw,
-                                          const float* __restrict__ kw, float eps,
-                                          const float* __restrict__ inv_freq, int rot,
-                                          const int* __restrict__ rope_pos,
+__global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, int S, size_t split_stride,
+                                          const float* __restrict__ qw, const float* __restrict__ kw,
+                                          float eps, const float2* __restrict__ cs, int rot,
                                           const int* __restrict__ cache_pos,
                                           const int* __restrict__ tok_seq,
                                           const int* __restrict__ block_table, int bt_stride,
                                           T* __restrict__ q_out, T* __restrict__ kcache,
                                           T* __restrict__ vcache, int nq, int nkv, int d, int layout) {
-    extern __shared__ float rowbuf[];  // [warps][d]
+    extern __shared__ __align__(16) float rowbuf[];  // [warps][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x;
     const int head = blockIdx.y * (blockDim.x >> 5) + warp;
@@ -144,7 +244,14 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const f
     if (head >= nheads) return;
     float* x = rowbuf + warp * d;
     const float* src = qkv + ((size_t)n * nheads + head) * d;
-    for (int e = lane; e < d; e += 32) x[e] = src[e];
+    for (int e = lane * 4; e < d; e += 128) {
+        float4 v = load4(src + e);
+        for (int s = 1; s < S; ++s) {
+            const float4 v2 = load4(src + s * split_stride + e);
+            v.x += v2.x; v.y += v2.y; v.z += v2.z; v.w += v2.w;
+        }
+        *reinterpret_cast<float4*>(x + e) = v;
+    }
     __syncwarp();
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
@@ -159,54 +266,57 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, const f
     }
     if ((is_q || is_k) && rot > 0) {
         const int half = rot >> 1;
-        const float pos = (float)rope_pos[n];
+        const float2* csn = cs + (size_t)n * half;
         for (int i = lane; i < half; i += 32) {
-            const float ang = pos * inv_freq[i];
-            float s, c;
-            sincosf(ang, &s, &c);
+            const float2 c_s = csn[i];
             const float a = x[i], b = x[i + half];
-            x[i] = a * c - b * s;
-            x[i + half] = a * s + b * c;
+            x[i] = a * c_s.x - b * c_s.y;
+            x[i + half] = a * c_s.y + b * c_s.x;
         }
         __syncwarp();
     }
     if (is_q) {
         T* dst = q_out + ((size_t)n * nq + head) * d;
-        for (int e = lane; e < d; e += 32) dst[e] = from_f32<T>(x[e]);
+        for (int e = lane * 4; e < d; e += 128) Pack4<T>::store(dst + e, x[e], x[e + 1], x[e + 2], x[e + 3]);
     } else {
         const int kvh = is_k ? head - nq : head - nq - nkv;
         const int cp = cache_pos[n];
         const int page = block_table[(size_t)tok_seq[n] * bt_stride + cp / LUMEN_PAGE];
         T* tile = (is_k ? kcache : vcache) + ((size_t)page * nkv + kvh) * LUMEN_PAGE * d;
         const int r = cp % LUMEN_PAGE;
-        for (int e = lane; e < d; e += 32) tile[tile_offset(layout, r, e, d)] = from_f32<T>(x[e]);
+        // groups of 4 values never straddle a 16-byte chunk, so they stay together in both layouts
+        for (int e = lane * 4; e < d; e += 128)
+            Pack4<T>::store(tile + tile_offset(layout, r, e, d), x[e], x[e + 1], x[e + 2], x[e + 3]);
     }
 }
 
-LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, const float* qw, const float* kw, float eps,
-                                       const float* inv_freq, int rot, const int* rope_pos,
-                                       const int* cache_pos, const int* tok_seq,
-                                       const int* block_table, int bt_stride, void* q_out,
-                                       void* kcache, void* vcache, int is_bf16, int N, int nq,
-                                       int nkv, int d, int layout, cudaStream_t stream) {
+LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, int n_splits, const float* qw, const float* kw,
+                                       float eps, const float* cs, int rot, const int* cache_pos,
+                                       const int* tok_seq, const int* block_table, int bt_stride,
+                                       void* q_out, void* kcache, void* vcache, int is_bf16, int N,
+                                       int nq, int nkv, int d, int layout, cudaStream_t stream) {
     if (N <= 0) return 0;
-    if (d <= 0 || d > QKR_MAX_D || (d & 1) || rot < 0 || rot > d || (rot & 1) || nq < 0 || nkv < 0)
+    if (d <= 0 || d > QKR_MAX_D || (d & 3) || rot < 0 || rot > d || (rot & 1) || nq < 0 || nkv < 0 ||
+        n_splits < 1)
         return LUMEN_ERR_UNSUPPORTED;
     if (layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64 != 0)) return LUMEN_ERR_UNSUPPORTED;
     if (layout != LUMEN_LAYOUT_SW128 && layout != LUMEN_LAYOUT_LINEAR) return LUMEN_ERR_BAD_ARGUMENT;
     const int warps = 4;
     const int nheads = nq + 2 * nkv;
     if (nheads == 0) return 0;
+    if ((nheads + warps - 1) / warps > 65535) return LUMEN_ERR_UNSUPPORTED;
     dim3 grid(N, (nheads + warps - 1) / warps);
     const size_t smem = (size_t)warps * d * sizeof(float);
+    const size_t stride = (size_t)N * nheads * d;
     if (is_bf16)
         qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
-            qkv, qw, kw, eps, inv_freq, rot, rope_pos, cache_pos, tok_seq, block_table, bt_stride,
-            (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nq, nkv, d, layout);
+            qkv, n_splits, stride, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
+            bt_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nq, nkv, d,
+            layout);
     else
         qk_norm_rope_store_kernel<float><<<grid, warps * 32, smem, stream>>>(
-            qkv, qw, kw, eps, inv_freq, rot, rope_pos, cache_pos, tok_seq, block_table, bt_stride,
-            (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, d, layout);
+            qkv, n_splits, stride, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
+            bt_stride, (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, d, layout);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -60,6 +60,7 @@ class DecoderModel:
 
     def forward(self, ctx: StepContext) -> torch.Tensor:
         """Logits float32 [W, V] at ctx.want_rows."""
+        ctx.extras.pop("per_step", None)     # tables that parts share within ONE step
         h = self.embedding.forward(ctx.tokens)
         pending = None
         needs = ctx.cache.group_of

@@ -1,6 +1,9 @@
 """Python faces of the hand-written kernels. Each function checks dtypes and
 shapes, launches on the current CUDA stream and returns its output tensor.
 Float32 tensors select the 32-bit variants, bfloat16 tensors the serving ones.
+
+A tensor that a split matrix product made may come as S partial results stacked
+in front, [S, rows, width]; the consumers below add the partials while reading.
 """
 from __future__ import annotations
 
@@ -8,7 +11,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from .native import KernelError, check, fn, ptr, require, stream_ptr
+from .native import KernelError, check, fn, library, ptr, require, stream_ptr
 
 P = c_void_p
 F32 = torch.float32
@@ -25,6 +28,16 @@ def _is_bf16(t) -> int:
     if t.dtype == F32:
         return 0
     raise KernelError(f"expected float32 or bfloat16, got {t.dtype}")
+
+
+def _partials(t, name):
+    """[rows, width] or [S, rows, width] -> (tensor as [S, rows, width], S)."""
+    require(t, F32, name)
+    if t.dim() == 2:
+        t = t.unsqueeze(0)
+    if t.dim() != 3:
+        raise KernelError(f"{name}: expected [rows, width] or [S, rows, width]")
+    return t, t.shape[0]
 
 
 def embed(tokens, table, out=None):
@@ -51,12 +64,10 @@ def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, write_h=True):
         raise KernelError(f"add_rmsnorm: weight has {weight.numel()} values, rows have {H}")
     S, stride = 0, 0
     if delta is not None:
-        require(delta, F32, "add_rmsnorm.delta")
-        if delta.dim() == 2:
-            delta = delta.unsqueeze(0)
+        delta, S = _partials(delta, "add_rmsnorm.delta")
         if tuple(delta.shape[1:]) != (N, H):
             raise KernelError(f"add_rmsnorm: delta {tuple(delta.shape)} does not match h {(N, H)}")
-        S, stride = delta.shape[0], N * H
+        stride = N * H
     n_rows = N
     if rows is not None:
         require(rows, I32, "add_rmsnorm.rows")
@@ -70,37 +81,49 @@ def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, write_h=True):
 
 
 def silu_mul(gu, out_dtype):
-    """z = silu(gu[:, :I]) * gu[:, I:]; gu float32 [N, 2I]."""
-    require(gu, F32, "silu_mul.gu")
-    N, I2 = gu.shape
+    """z = silu(gate) * up with gate = gu[..., :I], up = gu[..., I:]; gu float32 [N, 2I] or
+    [S, N, 2I] partials."""
+    gu, S = _partials(gu, "silu_mul.gu")
+    _, N, I2 = gu.shape
     if I2 % 2:
         raise KernelError("silu_mul: width must be even")
     z = torch.empty((N, I2 // 2), dtype=out_dtype, device=gu.device)
-    f = fn("core", "lumen_silu_mul", [P, P, c_int, c_int, c_int, P])
-    check(f(ptr(gu), ptr(z), _is_bf16(z), N, I2 // 2, stream_ptr()), "silu_mul")
+    f = fn("core", "lumen_silu_mul", [P, c_int, P, c_int, c_int, c_int, P])
+    check(f(ptr(gu), S, ptr(z), _is_bf16(z), N, I2 // 2, stream_ptr()), "silu_mul")
     return z
 
 
-def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, rope_pos, cache_pos,
-                       tok_seq, block_table, kcache, vcache, nq, nkv, d, out_dtype,
-                       layout=LAYOUT_LINEAR):
-    """Per-head RMSNorm of q and k, rotation, q out and k/v written to the paged cache.
-    qkv float32 [N, (nq + 2 nkv) d]; caches [pages, nkv, PAGE, d] of out_dtype
-    (None with nkv == 0: a layer that reads another layer's cache)."""
-    require(qkv, F32, "qk_norm_rope_store.qkv")
-    N = qkv.shape[0]
-    if qkv.shape[1] != (nq + 2 * nkv) * d:
-        raise KernelError(f"qk_norm_rope_store: row width {qkv.shape[1]} != (nq+2nkv)*d")
+def rope_table(positions, inv_freq):
+    """(cos, sin) of float32(pos) * inv_freq: float32 [N, rot/2, 2]."""
+    require(positions, I32, "rope_table.positions")
+    require(inv_freq, F32, "rope_table.inv_freq")
+    N, half = positions.numel(), inv_freq.numel()
+    cs = torch.empty((N, half, 2), dtype=F32, device=positions.device)
+    f = fn("core", "lumen_rope_table", [P, P, P, c_int, c_int, P])
+    check(f(ptr(positions), ptr(inv_freq), ptr(cs), N, half, stream_ptr()), "rope_table")
+    return cs
+
+
+def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, tok_seq,
+                       block_table, kcache, vcache, nq, nkv, d, out_dtype, layout=LAYOUT_LINEAR):
+    """Per-head RMSNorm of q and k, rotation by the angles of `cs` (from rope_table; None
+    with rotary_dim 0), q out and k/v written to the paged cache.
+    qkv float32 [N, (nq + 2 nkv) d] or [S, N, ...] partials; caches [pages, nkv, PAGE, d] of
+    out_dtype (None with nkv == 0: a layer that reads another layer's cache)."""
+    qkv, S = _partials(qkv, "qk_norm_rope_store.qkv")
+    N = qkv.shape[1]
+    if qkv.shape[2] != (nq + 2 * nkv) * d:
+        raise KernelError(f"qk_norm_rope_store: row width {qkv.shape[2]} != (nq+2nkv)*d")
     for t, nm in ((q_norm_w, "q_norm"), (k_norm_w, "k_norm")):
         if t is not None:
             require(t, F32, nm)
             if t.numel() != d:
                 raise KernelError(f"{nm} weight must have head_dim={d} values")
     if rotary_dim:
-        require(inv_freq, F32, "inv_freq")
-        if inv_freq.numel() != rotary_dim // 2:
-            raise KernelError("inv_freq must have rotary_dim/2 values")
-    for t, nm in ((rope_pos, "rope_pos"), (cache_pos, "cache_pos"), (tok_seq, "tok_seq")):
+        require(cs, F32, "rope angles")
+        if tuple(cs.shape) != (N, rotary_dim // 2, 2):
+            raise KernelError(f"rope angles must be [N, rotary_dim/2, 2], got {tuple(cs.shape)}")
+    for t, nm in ((cache_pos, "cache_pos"), (tok_seq, "tok_seq")):
         require(t, I32, nm)
         if t.numel() < N:
             raise KernelError(f"{nm} shorter than the token count")
@@ -110,10 +133,10 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, eps, inv_freq, rotary_dim, rope_
         require(kcache, out_dtype, "kcache")
         require(vcache, out_dtype, "vcache")
     f = fn("core", "lumen_qk_norm_rope_store",
-           [P, P, P, c_float, P, c_int, P, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int, c_int,
-            c_int, P])
-    check(f(ptr(qkv), ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(inv_freq), int(rotary_dim),
-            ptr(rope_pos), ptr(cache_pos), ptr(tok_seq), ptr(block_table), block_table.stride(0),
+           [P, c_int, P, P, c_float, P, c_int, P, P, P, c_int, P, P, P, c_int, c_int, c_int, c_int,
+            c_int, c_int, P])
+    check(f(ptr(qkv), S, ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(cs), int(rotary_dim),
+            ptr(cache_pos), ptr(tok_seq), ptr(block_table), block_table.stride(0),
             ptr(q_out), ptr(kcache), ptr(vcache), _is_bf16(q_out), N, nq, nkv, d, int(layout),
             stream_ptr()),
           "qk_norm_rope_store")
@@ -155,6 +178,41 @@ def gemm_f32(a, w, out=None):
         out = torch.empty((M, N), dtype=F32, device=a.device)
     f = fn("gemm_f32", "lumen_gemm_f32", [P, P, c_int, P, c_int, c_int, c_int, P])
     check(f(ptr(a), ptr(w), _is_bf16(w), ptr(out), M, N, K, stream_ptr()), "gemm_f32")
+    return out
+
+
+SMALL_M = 16   # the weight-streaming product takes up to this many rows
+
+
+def gemm_small_splits(N, K) -> int:
+    f = library("gemm_small").lumen_gemm_small_splits
+    f.restype = c_int
+    f.argtypes = [c_int, c_int]
+    return int(f(int(N), int(K)))
+
+
+def gemm_small(x, w, silu_gate_up=False):
+    """Weight-streaming product for M <= 16 rows: float32 partials [S, M, N] of x @ w.T.
+    x bfloat16 [M, K]; or, with silu_gate_up, float32 [M, 2K] holding gate | up, of which
+    silu(gate) * up is multiplied. w bfloat16 [N, K], K a multiple of 8."""
+    require(w, BF16, "gemm_small.w")
+    N, K = w.shape
+    xs = 1
+    if silu_gate_up:
+        x, xs = _partials(x, "gemm_small.x")
+        if x.shape[2] != 2 * K:
+            raise KernelError(f"gemm_small: gate|up input must be [M, {2 * K}] or [S, M, {2 * K}]")
+        M = x.shape[1]
+    else:
+        require(x, BF16, "gemm_small.x")
+        if x.dim() != 2 or x.shape[1] != K:
+            raise KernelError(f"gemm_small: inner sizes differ ({x.shape[1]} vs {K})")
+        M = x.shape[0]
+    S = gemm_small_splits(N, K)
+    out = torch.empty((S, M, N), dtype=F32, device=x.device)
+    f = fn("gemm_small", "lumen_gemm_small", [P, c_int, c_int, P, P, c_int, c_int, c_int, P])
+    check(f(ptr(x), 1 if silu_gate_up else 0, xs, ptr(w), ptr(out), M, N, K, stream_ptr()),
+          "gemm_small")
     return out
 
 

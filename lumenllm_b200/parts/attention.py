@@ -80,11 +80,12 @@ class GQAttention:
     def forward(self, y, ctx, entry):
         kc, vc, table = entry.cache()
         writes = entry.writes_cache and not self.shares_cache
-        qkv = self.qkv(y) if writes else self.q_only(y)       # float32 [N, (nq + 2 nkv) d]
+        # float32 [N, (nq + 2 nkv) d], possibly as S partial sums
+        qkv = self.qkv(y, split_ok=True) if writes else self.q_only(y, split_ok=True)
         nkv_new = self.nkv if writes else 0
         q = K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, self.qk_eps,
-                                 self.position.inv_freq, self.position.rotary_dim,
-                                 ctx.rope_pos, ctx.cache_pos, ctx.tok_seq, table,
+                                 self.position.angles(ctx), self.position.rotary_dim,
+                                 ctx.cache_pos, ctx.tok_seq, table,
                                  kc if nkv_new else None, vc if nkv_new else None,
                                  self.nq, nkv_new, self.d, self.runtime.dtype, layout=entry.layout)
         out = self.attend(q, kc, vc, table, ctx, entry.layout)

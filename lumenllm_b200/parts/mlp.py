@@ -6,6 +6,7 @@ Gate and up weights are stacked so that both cost one product.
 """
 from __future__ import annotations
 
+from ..ops import gemm as G
 from ..ops import kernels as K
 from .base import need, register_part
 from .linear import Linear
@@ -29,9 +30,12 @@ class SwiGLU:
         self.gate_up = Linear.stacked([weights[f"{pre}.gate_proj.weight"],
                                        weights[f"{pre}.up_proj.weight"]], runtime)
         self.down = Linear(weights[f"{pre}.down_proj.weight"], runtime)
-        self.z_dtype = self.runtime.dtype if not self.down.f32 else self.runtime.dtype
 
     def forward(self, y, ctx):
-        gu = self.gate_up(y)                       # float32 [N, 2I]
+        gu = self.gate_up(y, split_ok=True)        # float32 [N, 2I], possibly S partials
+        if not self.down.f32:
+            out = G.gemm_bf16_silu_gate_up(gu, self.down.weight)   # few rows: one kernel
+            if out is not None:
+                return out
         z = K.silu_mul(gu, self.runtime.dtype)
         return self.down(z, split_ok=True)

@@ -68,6 +68,10 @@ def test_silu_mul(out_dtype):
     z = K.silu_mul(dev(gu), out_dtype).cpu().float()
     tol = 1e-6 if out_dtype == F32 else 2 ** -8
     assert float(((z - ref).abs() / (1 + ref.abs())).max()) < tol
+    z2 = K.silu_mul(dev(torch.stack([0.5 * gu, 0.5 * gu])), out_dtype).cpu().float()
+    assert torch.equal(z, z2)            # halves add up exactly
+    odd = torch.randn(3, 2 * 7, generator=gen(22))           # a width that is no multiple of 4
+    assert torch.allclose(K.silu_mul(dev(odd), F32).cpu(), P.swiglu(odd[:, :7], odd[:, 7:]), atol=1e-6)
 
 
 def to_sw128(x):
@@ -105,7 +109,11 @@ def test_qk_norm_rope_store(dtype, nq, nkv, d, rot):
     kc = torch.zeros(n_pages, nkv, 64, d, dtype=dtype)
     vc = torch.zeros_like(kc)
     kcd, vcd = dev(kc), dev(vc)
-    q = K.qk_norm_rope_store(dev(qkv), dev(qw), dev(kw), eps, dev(inv), rot, dev(pos), dev(pos),
+    cs = K.rope_table(dev(pos), dev(inv))
+    assert torch.allclose(cs.cpu()[..., 0], torch.cos(pos.float()[:, None] * inv[None, :]), atol=2e-6)
+    # the projection may arrive as partial sums: split it in three unequal parts
+    parts = torch.stack([0.5 * qkv, 0.25 * qkv, 0.25 * qkv])
+    q = K.qk_norm_rope_store(dev(parts), dev(qw), dev(kw), eps, cs, rot, dev(pos),
                              dev(seq), dev(table), kcd, vcd, nq, nkv, d, dtype).cpu().float()
     x = qkv.view(N, nq + 2 * nkv, d)
     qr = P.apply_rope(P.rms_norm(x[:, :nq], qw, eps), pos, theta, rot)
@@ -125,7 +133,7 @@ def test_qk_norm_rope_store(dtype, nq, nkv, d, rot):
         if pg not in used:
             assert float(kg[pg].abs().max()) == 0.0
     # without norm weights and without rotation the values pass through
-    q2 = K.qk_norm_rope_store(dev(qkv), None, None, eps, None, 0, dev(pos), dev(pos), dev(seq),
+    q2 = K.qk_norm_rope_store(dev(qkv), None, None, eps, None, 0, dev(pos), dev(seq),
                               dev(table), kcd, vcd, nq, nkv, d, dtype).cpu().float()
     assert rel(q2, x[:, :nq]) < tol
 
@@ -230,7 +238,7 @@ def test_swizzled_writer_and_reader_agree():
     for layout in (K.LAYOUT_LINEAR, K.LAYOUT_SW128):
         kc = torch.zeros(9, nkv, 64, d, dtype=BF16).cuda()
         vc = torch.zeros_like(kc)
-        q = K.qk_norm_rope_store(dev(qkv), None, None, 0.0, None, 0, dev(pos), dev(pos), dev(seq),
+        q = K.qk_norm_rope_store(dev(qkv), None, None, 0.0, None, 0, dev(pos), dev(seq),
                                  dev(table), kc, vc, nq, nkv, d, BF16, layout=layout)
         outs.append(K.attn_generic(q, kc, vc, dev(table), dev(seq), dev(pos), 0, d ** -0.5,
                                    layout=layout).cpu())
@@ -327,6 +335,39 @@ def test_gemm_f32_is_true_float32(wdtype, M, N, K_):
     # a row's result does not depend on the other rows of the batch
     one = K.gemm_f32(dev(a[M // 2:M // 2 + 1].contiguous()), dev(w)).cpu()
     assert torch.equal(one[0], out[M // 2])
+
+
+@pytest.mark.parametrize("M,N,K_", [(1, 4096, 4096), (8, 6144, 4096), (3, 311, 80), (16, 130, 1000),
+                                    (9, 24576, 512), (5, 96, 12288), (2, 16, 8)])
+def test_gemm_small_streams_weights(M, N, K_):
+    """The few-row product: against float64 of the same bfloat16 inputs; a row's result does
+    not depend on the batch; the k splits depend on the weight's shape only."""
+    from lumenllm_b200.ops import kernels as K
+    g = gen(14)
+    x = torch.randn(M, K_, generator=g).to(BF16)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(BF16)
+    part = K.gemm_small(dev(x), dev(w)).cpu()
+    assert part.shape == (K.gemm_small_splits(N, K_), M, N)
+    out = part.sum(0)
+    ref = x.double() @ w.double().T
+    assert float((out.double() - ref).abs().max()) < 1e-4
+    one = K.gemm_small(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w)).cpu()
+    assert torch.equal(one[:, 0], part[:, M // 2])
+
+
+@pytest.mark.parametrize("M,I,H", [(4, 12288, 256), (16, 176, 80), (1, 512, 96)])
+def test_gemm_small_with_silu_prologue(M, I, H):
+    from lumenllm_b200.ops import kernels as K
+    g = gen(15)
+    gu = torch.randn(M, 2 * I, generator=g)
+    w = (torch.randn(H, I, generator=g) / math.sqrt(I)).to(BF16)
+    z = P.swiglu(gu[:, :I], gu[:, I:]).to(BF16)
+    ref = z.double() @ w.double().T
+    out = K.gemm_small(dev(gu), dev(w), silu_gate_up=True).cpu().sum(0)
+    assert float((out.double() - ref).abs().max()) < 2e-3 * max(1.0, float(ref.abs().max()))
+    halves = torch.stack([0.5 * gu, 0.5 * gu])
+    out2 = K.gemm_small(dev(halves), dev(w), silu_gate_up=True).cpu().sum(0)
+    assert torch.equal(out, out2)
 
 
 def test_argmax_ties_and_odd_vocab():
