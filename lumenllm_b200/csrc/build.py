@@ -29,6 +29,7 @@ MODULES = {
     "core": (["core.cu"], ["common.cuh"]),
     "gemm_f32": (["gemm_f32.cu"], ["common.cuh"]),
     "gemm_small": (["gemm_small.cu"], ["common.cuh", "mma_utils.cuh"]),
+    "gemm_tc": (["gemm_tc.cu"], ["common.cuh", "mma_utils.cuh"]),
     "attn_generic": (["attn_generic.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),
     "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "attn_decode_noalloc.h"]),

@@ -142,13 +142,26 @@ LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long 
 }
 
 // ---------------------------------------------------------------- SiLU(gate) * up
-// gu: [S, N, 2*I] float32 partials with the gate in columns [0, I) and up in [I, 2I).
+// gu: [S, N, 2*I] float32 partials with the gate in columns [0, I) and up in [I, 2I); or,
+// interleaved, gate_i in column 2i and up_i in column 2i + 1.
 template <typename TOut>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int S, size_t split_stride,
-                                TOut* __restrict__ z, long long total, int I) {
+                                TOut* __restrict__ z, long long total, int I, int interleaved) {
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long step = (long long)gridDim.x * blockDim.x;
-    if ((I & 3) == 0) {
+    if (interleaved) {
+        for (; idx < total; idx += step) {
+            const long long n = idx / I;
+            const int i = (int)(idx - n * I);
+            const float* gp = gu + n * 2 * I + 2 * i;
+            float2 v = *reinterpret_cast<const float2*>(gp);
+            for (int s = 1; s < S; ++s) {
+                const float2 v2 = *reinterpret_cast<const float2*>(gp + s * split_stride);
+                v.x += v2.x; v.y += v2.y;
+            }
+            z[idx] = from_f32<TOut>(v.x / (1.0f + expf(-v.x)) * v.y);
+        }
+    } else if ((I & 3) == 0) {
         const long long total4 = total >> 2;
         const int I4 = I >> 2;
         for (; idx < total4; idx += step) {
@@ -179,19 +192,20 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int S, size_t spli
 }
 
 LUMEN_API int lumen_silu_mul(const float* gu, int n_splits, void* z, int z_is_bf16, int N, int I,
-                             cudaStream_t stream) {
+                             int interleaved, cudaStream_t stream) {
     if (N <= 0) return 0;
     if (I <= 0 || n_splits < 1) return LUMEN_ERR_BAD_ARGUMENT;
     const long long total = (long long)N * I;
     const size_t stride = (size_t)N * 2 * I;
-    long long blocks = (total / 4 + 255) / 256;
+    long long blocks = ((interleaved ? total : total / 4) + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
     if (z_is_bf16)
         silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(gu, n_splits, stride,
-                                                                       (__nv_bfloat16*)z, total, I);
+                                                                       (__nv_bfloat16*)z, total, I, interleaved);
     else
-        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>(gu, n_splits, stride, (float*)z, total, I);
+        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>(gu, n_splits, stride, (float*)z, total, I,
+                                                                interleaved);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -38,6 +38,7 @@ __device__ __forceinline__ uint32_t u4_get(const uint4& v, int j) {
 //   MODE 0: x is bfloat16 [M, K].
 //   MODE 1: x is float32 [XS, M, 2K], XS partial sums of gate | up (added in rising order);
 //           the staged value is silu(gate) * up.
+//   MODE 2: as MODE 1, but gate_i and up_i alternate: columns 2i and 2i + 1.
 template <int MODE>
 __device__ __forceinline__ void stage_x(const void* x, int XS, __nv_bfloat16* xs, int M, int MP, int K,
                                         int k0, int klen, int xstride) {
@@ -48,6 +49,24 @@ __device__ __forceinline__ void stage_x(const void* x, int XS, __nv_bfloat16* xs
         if (m < M) {
             if (MODE == 0) {
                 v = *reinterpret_cast<const uint4*>((const __nv_bfloat16*)x + (size_t)m * K + k0 + 8 * c);
+            } else if (MODE == 2) {
+                const float* src = (const float*)x + (size_t)m * 2 * K + 2 * (k0 + 8 * c);
+                float4 q[4];
+#pragma unroll
+                for (int i = 0; i < 4; ++i) q[i] = *reinterpret_cast<const float4*>(src + 4 * i);
+                for (int s = 1; s < XS; ++s) {
+                    const size_t o = (size_t)s * M * 2 * K;
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) {
+                        const float4 a = *reinterpret_cast<const float4*>(src + o + 4 * i);
+                        q[i].x += a.x; q[i].y += a.y; q[i].z += a.z; q[i].w += a.w;
+                    }
+                }
+                auto f = [](float a, float b) { return a / (1.0f + expf(-a)) * b; };
+                v.x = pack_bf16(f(q[0].x, q[0].y), f(q[0].z, q[0].w));
+                v.y = pack_bf16(f(q[1].x, q[1].y), f(q[1].z, q[1].w));
+                v.z = pack_bf16(f(q[2].x, q[2].y), f(q[2].z, q[2].w));
+                v.w = pack_bf16(f(q[3].x, q[3].y), f(q[3].z, q[3].w));
             } else {
                 const float* g = (const float*)x + (size_t)m * 2 * K + k0 + 8 * c;
                 const float* u = g + K;
@@ -171,12 +190,13 @@ LUMEN_API int lumen_gemm_small_splits(int N, int K) {
 }
 
 // x: mode 0 bfloat16 [M, K]; mode 1 float32 [x_splits, M, 2K] (partials of gate | up;
-// SiLU(gate)*up is applied to their sum). out: float32 [S, M, N] with
+// SiLU(gate)*up is applied to their sum); mode 2 the same with gate_i, up_i in columns
+// 2i, 2i + 1. out: float32 [S, M, N] with
 // S = lumen_gemm_small_splits(N, K).
 LUMEN_API int lumen_gemm_small(const void* x, int mode, int x_splits, const void* W, float* out, int M,
                                int N, int K, cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (M > 16 || K <= 0 || (K & 7) || (mode != 0 && mode != 1) || x_splits < 1) return LUMEN_ERR_UNSUPPORTED;
+    if (M > 16 || K <= 0 || (K & 7) || mode < 0 || mode > 2 || x_splits < 1) return LUMEN_ERR_UNSUPPORTED;
     const int S = lumen_gemm_small_splits(N, K);
     const int slice = ((K + S - 1) / S + 63) & ~63;
     const int NT = (M + 7) / 8;
@@ -192,9 +212,11 @@ LUMEN_API int lumen_gemm_small(const void* x, int mode, int x_splits, const void
         k<<<grid, GS_THREADS, smem, stream>>>(x, Wp, out, M, N, K, slice, x_splits);               \
     } while (0)
     if (NT == 1 && mode == 0) GS_LAUNCH(1, 0);
-    else if (NT == 1) GS_LAUNCH(1, 1);
+    else if (NT == 1 && mode == 1) GS_LAUNCH(1, 1);
+    else if (NT == 1) GS_LAUNCH(1, 2);
     else if (mode == 0) GS_LAUNCH(2, 0);
-    else GS_LAUNCH(2, 1);
+    else if (mode == 1) GS_LAUNCH(2, 1);
+    else GS_LAUNCH(2, 2);
 #undef GS_LAUNCH
     LUMEN_LAUNCH_CHECK();
     return 0;

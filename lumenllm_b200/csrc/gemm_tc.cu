@@ -1,0 +1,404 @@
+// bfloat16 matrix product on the 5th-generation tensor cores: D[a, b] = sum_k A[a, k] B[b, k],
+// both operands row-major with k contiguous ("K-major"), float32 accumulation in tensor memory.
+//
+//   * Operands reach shared memory by TMA (cp.async.bulk.tensor, 128-byte swizzle, one
+//     64-wide k block per stage, no multicast), complete on mbarriers, and are consumed in
+//     place by tcgen05.mma through shared-memory descriptors; one thread issues the MMAs.
+//   * The accumulator of a 128 x BN tile lives in tensor memory; there are two of them, so
+//     the epilogue of one tile (tcgen05.ld -> registers -> global) overlaps the next tile's
+//     main loop.
+//   * One persistent block per SM walks the list of tiles (static round robin). Warp 0
+//     produces (TMA), warp 1 allocates tensor memory and issues the MMAs, warps 2..5 are the
+//     epilogue (their index mod 4 selects the 32 lanes of tensor memory each may read).
+//
+// Two orientations share the code. With many rows of activations (prompts) A = activations and
+// B = weights, BN = 256. With few rows (decode) the roles are swapped: A = weights, so that the
+// 128-row side of the MMA is filled by weight rows, and B = the activations padded to 16/32/64
+// rows; the product is then a stream over the weights with a deep TMA ring, and k may be split
+// over several tiles so that all SMs pull from HBM. A split writes partial sums [S, M, N] that
+// the consumer adds in rising order; S depends on the weight's shape only.
+//
+// Epilogues: float32 out; or, for a weight whose rows alternate gate_i, up_i, SiLU(gate)*up
+// written as bfloat16 (no split then).
+//
+// Every wait is bounded: when one runs out the block raises an error flag, stops issuing work,
+// lets the other roles run out likewise, frees its tensor memory and returns.
+#include <cuda.h>
+
+#include "common.cuh"
+#include "mma_utils.cuh"
+
+#define TC_BM 128
+#define TC_BK 64
+#define TC_THREADS 192
+#define TC_EPI_F32 0
+#define TC_EPI_SILU 1
+
+__device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
+}
+__device__ __forceinline__ void tma_load_2d(void* dst, const CUtensorMap* map, int c0, int c1, uint64_t* bar) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];" ::"r"(
+            smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(smem_u32(bar)), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar))
+                 : "memory");
+}
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                       uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, float (&v)[16]) {
+    uint32_t r[16];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
+}
+
+// Shared-memory descriptor of a K-major tile in the 128-byte swizzle: rows of 128 bytes,
+// groups of 8 rows 1024 bytes apart (stride byte offset), version 1, layout type 2.
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= (uint64_t)((smem_addr >> 4) & 0x3FFF);
+    d |= (uint64_t)1 << 16;                 // leading byte offset (unused with swizzle): 1
+    d |= (uint64_t)(1024 >> 4) << 32;       // stride byte offset
+    d |= (uint64_t)1 << 46;                 // descriptor version
+    d |= (uint64_t)2 << 61;                 // SWIZZLE_128B
+    return d;
+}
+// Instruction descriptor: D float32, A and B bfloat16, both K-major, M = 128, N = BN.
+__host__ __device__ constexpr uint32_t tc_idesc(int bn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+}
+
+struct TcParams {
+    float* out_f32;           // EPI_F32: [S, M, N]
+    __nv_bfloat16* out_bf16;  // EPI_SILU: [M, N / 2]
+    int M, N;                 // rows of activations, rows of the weight
+    int rowsA, rowsB;         // rows of the A and of the B operand
+    int num_kb;               // 64-wide k blocks in K
+    int splits, kb_per_split;
+    int* err;
+};
+
+template <int BN, int STAGES, bool SWAP, int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+               const TcParams p) {
+    constexpr int A_BYTES = TC_BM * 128, B_BYTES = BN * 128;
+    constexpr int NCOLS = (2 * BN < 32) ? 32 : 2 * BN;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    // operand tiles must start on 1024-byte boundaries (the swizzle pattern repeats there)
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + STAGES * A_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * B_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* tempty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int tilesA = (p.rowsA + TC_BM - 1) / TC_BM, tilesB = (p.rowsB + BN - 1) / BN;
+    const int n_items = tilesA * tilesB * p.splits;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 4); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(NCOLS)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+
+    // item -> (tile of A, tile of B, split); tiles of A vary fastest so that blocks working at
+    // the same time share their B tile through L2
+    auto decode = [&](int item, int& ta, int& tb, int& s) {
+        s = item % p.splits;
+        const int t = item / p.splits;
+        ta = t % tilesA;
+        tb = t / tilesA;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
+                int ta, tb, s;
+                decode(item, ta, tb, s);
+                const int kb0 = s * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int st = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
+                    mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
+                    tma_load_2d(sA + st * A_BYTES, &tmA, kb * TC_BK, ta * TC_BM, &full[st]);
+                    tma_load_2d(sB + st * B_BYTES, &tmB, kb * TC_BK, tb * BN, &full[st]);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            constexpr uint32_t idesc = tc_idesc(BN);
+            int it = 0, acc_it = 0;
+            for (int item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x, ++acc_it) {
+                int ta, tb, s;
+                decode(item, ta, tb, s);
+                const int kb0 = s * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.num_kb);
+                const int acc = acc_it & 1, aph = (acc_it >> 1) & 1;
+                if (!mbar_wait(&tempty[acc], aph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * BN;
+                bool ok = true;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int st = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait(&full[st], ph)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t ad = tc_smem_desc(smem_u32(sA + st * A_BYTES));
+                    const uint64_t bd = tc_smem_desc(smem_u32(sB + st * B_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)   // 16 values of k = 32 bytes = 2 units of 16 bytes
+                        tc_mma(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb > kb0 || k > 0) ? 1u : 0u);
+                    tc_commit(&empty[st]);     // the stage is free once these MMAs have read it
+                }
+                if (!ok) { *abort_flag = 1; atomicExch(p.err, 1); break; }
+                tc_commit(&tfull[acc]);        // the accumulator is complete once all MMAs are done
+            }
+        }
+    } else {
+        const int q = warp & 3;                // lanes of tensor memory this warp may read
+        const int row_in_tile = q * 32 + lane;
+        int acc_it = 0;
+        for (int item = blockIdx.x; item < n_items; item += gridDim.x, ++acc_it) {
+            // one decision per warp: the loads below are warp-wide instructions
+            if (__any_sync(0xffffffffu, *abort_flag != 0)) break;
+            int ta, tb, s;
+            decode(item, ta, tb, s);
+            const int acc = acc_it & 1, aph = (acc_it >> 1) & 1;
+            bool ok = mbar_wait(&tfull[acc], aph);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(p.err, 1); break; }
+            tc_fence_after();
+            const int a = ta * TC_BM + row_in_tile;                 // row of the A operand
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
+#pragma unroll 1
+            for (int c0 = 0; c0 < BN; c0 += 16) {
+                float v[16];
+                tc_ld16(taddr0 + c0, v);
+                const int b0 = tb * BN + c0;                        // first row of the B operand
+                if (EPI == TC_EPI_F32) {
+                    float* o = p.out_f32 + (size_t)s * p.M * p.N;
+                    if (!SWAP) {            // a = activation row m, b = weight row n
+                        if (a < p.M) {
+                            float* dst = o + (size_t)a * p.N + b0;
+                            if ((p.N & 3) == 0 && b0 + 16 <= p.N) {
+#pragma unroll
+                                for (int j = 0; j < 16; j += 4)
+                                    *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 16; ++j)
+                                    if (b0 + j < p.N) dst[j] = v[j];
+                            }
+                        }
+                    } else {                // a = weight row n, b = activation row m
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (a < p.N && b0 + j < p.M) o[(size_t)(b0 + j) * p.N + a] = v[j];
+                    }
+                } else {
+                    const int half = p.N >> 1;
+                    if (!SWAP) {            // columns 2i, 2i+1 of this thread are gate_i, up_i
+                        if (a < p.M) {
+                            __nv_bfloat16* dst = p.out_bf16 + (size_t)a * half + (b0 >> 1);
+                            float z[8];
+#pragma unroll
+                            for (int j = 0; j < 8; ++j) z[j] = v[2 * j] / (1.0f + expf(-v[2 * j])) * v[2 * j + 1];
+                            if ((half & 7) == 0 && b0 + 16 <= p.N) {
+                                uint4 w;
+                                w.x = pack_bf16(z[0], z[1]); w.y = pack_bf16(z[2], z[3]);
+                                w.z = pack_bf16(z[4], z[5]); w.w = pack_bf16(z[6], z[7]);
+                                *reinterpret_cast<uint4*>(dst) = w;
+                            } else {
+#pragma unroll
+                                for (int j = 0; j < 8; ++j)
+                                    if (b0 + 2 * j + 1 < p.N) dst[j] = __float2bfloat16_rn(z[j]);
+                            }
+                        }
+                    } else {                // lanes 2i, 2i+1 hold gate_i, up_i of every column
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) {
+                            const float up = __shfl_xor_sync(0xffffffffu, v[j], 1);
+                            if ((lane & 1) == 0 && a + 1 < p.N && b0 + j < p.M)
+                                p.out_bf16[(size_t)(b0 + j) * half + (a >> 1)] =
+                                    __float2bfloat16_rn(v[j] / (1.0f + expf(-v[j])) * up);
+                        }
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&tempty[acc]);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(NCOLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------------------------ host
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*,
+                                  CUtensorMapInterleave, CUtensorMapSwizzle, CUtensorMapL2promotion,
+                                  CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (!fn) {
+        void* ptr = nullptr;
+        cudaDriverEntryPointQueryResult res;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &ptr, cudaEnableDefault, &res) == cudaSuccess &&
+            res == cudaDriverEntryPointSuccess)
+            fn = (EncodeTiledFn)ptr;
+    }
+    return fn;
+}
+
+// Map of a row-major bfloat16 matrix [rows, K] with boxes of box_rows x 64 values, 128-byte
+// swizzle, zeros outside the matrix.
+static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return LUMEN_ERR_UNSUPPORTED;
+    cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)K * 2};
+    cuuint32_t box[2] = {TC_BK, (cuuint32_t)box_rows};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
+                    CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                    CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : LUMEN_ERR_BAD_ARGUMENT;
+}
+
+static int sm_count() {
+    static int n = 0;
+    if (!n) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, dev);
+        if (n <= 0) n = 148;
+    }
+    return n;
+}
+
+// Few rows use the swapped orientation.
+static bool tc_swapped(int M) { return M <= 64; }
+
+// Number of k splits: a function of the weight's shape (and of the orientation) only. For the
+// swapped orientation the split that fills the SMs most evenly is chosen, small splits first.
+LUMEN_API int lumen_gemm_tc_splits(int M, int N, int K, int epi) {
+    if (epi == TC_EPI_SILU || !tc_swapped(M)) return 1;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const int tiles = (N + TC_BM - 1) / TC_BM;
+    const int sms = 148;   // fixed, so that the split never depends on the device at hand
+    int best = 1;
+    double best_eff = 0.0;
+    for (int s = 1; s <= 16 && s <= num_kb; ++s) {
+        if (num_kb / s < 4) break;              // keep at least 4 k blocks per tile
+        const int items = tiles * s;
+        const double eff = (double)items / (double)(((items + sms - 1) / sms) * sms);
+        if (eff > best_eff + 0.03) { best_eff = eff; best = s; }
+    }
+    const int per = (num_kb + best - 1) / best;
+    return (num_kb + per - 1) / per;
+}
+
+template <int BN, int STAGES, bool SWAP, int EPI>
+static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)STAGES * (TC_BM * 128 + BN * 128) + (2 * STAGES + 4) * 8 + 16 + 1024;
+    auto k = gemm_tc_kernel<BN, STAGES, SWAP, EPI>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const int tilesA = (p.rowsA + TC_BM - 1) / TC_BM, tilesB = (p.rowsB + BN - 1) / BN;
+    const int items = tilesA * tilesB * p.splits;
+    const int grid = items < sm_count() ? items : sm_count();
+    k<<<grid, TC_THREADS, smem, stream>>>(ma, mb, p);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// x bfloat16 [M, K]; W bfloat16 [N, K]; K a multiple of 8; both 16-byte aligned.
+// epi 0: out float32 [S, M, N], S = lumen_gemm_tc_splits(M, N, K, 0).
+// epi 1: W's rows alternate gate_i, up_i; out bfloat16 [M, N / 2] = SiLU(gate) * up.
+LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int epi, int* err,
+                            cudaStream_t stream) {
+    if (M <= 0 || N <= 0) return 0;
+    if (K <= 0 || (K & 7) || (epi != TC_EPI_F32 && epi != TC_EPI_SILU)) return LUMEN_ERR_UNSUPPORTED;
+    if (epi == TC_EPI_SILU && (N & 1)) return LUMEN_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return LUMEN_ERR_BAD_ARGUMENT;
+    TcParams p;
+    p.out_f32 = (float*)out;
+    p.out_bf16 = (__nv_bfloat16*)out;
+    p.M = M;
+    p.N = N;
+    p.num_kb = (K + TC_BK - 1) / TC_BK;
+    p.splits = lumen_gemm_tc_splits(M, N, K, epi);
+    p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
+    p.err = err;
+    CUtensorMap ma, mb;
+    int rc;
+    if (tc_swapped(M)) {
+        const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
+        p.rowsA = N;
+        p.rowsB = M;
+        if ((rc = make_map(&ma, W, N, K, TC_BM))) return rc;
+        if ((rc = make_map(&mb, x, M, K, bn))) return rc;
+        if (epi == TC_EPI_F32) {
+            if (bn == 16) return tc_launch<16, 10, true, TC_EPI_F32>(ma, mb, p, stream);
+            if (bn == 32) return tc_launch<32, 9, true, TC_EPI_F32>(ma, mb, p, stream);
+            return tc_launch<64, 8, true, TC_EPI_F32>(ma, mb, p, stream);
+        }
+        if (bn == 16) return tc_launch<16, 10, true, TC_EPI_SILU>(ma, mb, p, stream);
+        if (bn == 32) return tc_launch<32, 9, true, TC_EPI_SILU>(ma, mb, p, stream);
+        return tc_launch<64, 8, true, TC_EPI_SILU>(ma, mb, p, stream);
+    }
+    p.rowsA = M;
+    p.rowsB = N;
+    if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
+    if ((rc = make_map(&mb, W, N, K, 256))) return rc;
+    if (epi == TC_EPI_F32) return tc_launch<256, 4, false, TC_EPI_F32>(ma, mb, p, stream);
+    return tc_launch<256, 4, false, TC_EPI_SILU>(ma, mb, p, stream);
+}

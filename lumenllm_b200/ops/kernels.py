@@ -80,16 +80,17 @@ def add_rmsnorm(h, delta, weight, eps, out_dtype, rows=None, write_h=True):
     return y
 
 
-def silu_mul(gu, out_dtype):
-    """z = silu(gate) * up with gate = gu[..., :I], up = gu[..., I:]; gu float32 [N, 2I] or
-    [S, N, 2I] partials."""
+def silu_mul(gu, out_dtype, interleaved=False):
+    """z = silu(gate) * up with gate = gu[..., :I], up = gu[..., I:] (or, interleaved,
+    gate_i = gu[..., 2i], up_i = gu[..., 2i+1]); gu float32 [N, 2I] or [S, N, 2I] partials."""
     gu, S = _partials(gu, "silu_mul.gu")
     _, N, I2 = gu.shape
     if I2 % 2:
         raise KernelError("silu_mul: width must be even")
     z = torch.empty((N, I2 // 2), dtype=out_dtype, device=gu.device)
-    f = fn("core", "lumen_silu_mul", [P, c_int, P, c_int, c_int, c_int, P])
-    check(f(ptr(gu), S, ptr(z), _is_bf16(z), N, I2 // 2, stream_ptr()), "silu_mul")
+    f = fn("core", "lumen_silu_mul", [P, c_int, P, c_int, c_int, c_int, c_int, P])
+    check(f(ptr(gu), S, ptr(z), _is_bf16(z), N, I2 // 2, 1 if interleaved else 0, stream_ptr()),
+          "silu_mul")
     return z
 
 
@@ -191,10 +192,11 @@ def gemm_small_splits(N, K) -> int:
     return int(f(int(N), int(K)))
 
 
-def gemm_small(x, w, silu_gate_up=False):
+def gemm_small(x, w, silu_gate_up=False, interleaved=False):
     """Weight-streaming product for M <= 16 rows: float32 partials [S, M, N] of x @ w.T.
-    x bfloat16 [M, K]; or, with silu_gate_up, float32 [M, 2K] holding gate | up, of which
-    silu(gate) * up is multiplied. w bfloat16 [N, K], K a multiple of 8."""
+    x bfloat16 [M, K]; or, with silu_gate_up, float32 [M, 2K] holding gate | up (interleaved:
+    gate_i, up_i in columns 2i, 2i+1), of which silu(gate) * up is multiplied.
+    w bfloat16 [N, K], K a multiple of 8."""
     require(w, BF16, "gemm_small.w")
     N, K = w.shape
     xs = 1
@@ -211,8 +213,37 @@ def gemm_small(x, w, silu_gate_up=False):
     S = gemm_small_splits(N, K)
     out = torch.empty((S, M, N), dtype=F32, device=x.device)
     f = fn("gemm_small", "lumen_gemm_small", [P, c_int, c_int, P, P, c_int, c_int, c_int, P])
-    check(f(ptr(x), 1 if silu_gate_up else 0, xs, ptr(w), ptr(out), M, N, K, stream_ptr()),
-          "gemm_small")
+    mode = 0 if not silu_gate_up else (2 if interleaved else 1)
+    check(f(ptr(x), mode, xs, ptr(w), ptr(out), M, N, K, stream_ptr()), "gemm_small")
+    return out
+
+
+def gemm_tc_splits(M, N, K, silu=False) -> int:
+    f = library("gemm_tc").lumen_gemm_tc_splits
+    f.restype = c_int
+    f.argtypes = [c_int, c_int, c_int, c_int]
+    return int(f(int(M), int(N), int(K), 1 if silu else 0))
+
+
+def gemm_tc(x, w, silu_interleaved=False):
+    """x @ w.T on the tcgen05 tensor cores. x bfloat16 [M, K], w bfloat16 [N, K], K a
+    multiple of 8. Returns float32 partials [S, M, N] (S = 1 unless M <= 64); or, with
+    silu_interleaved (rows of w alternate gate_i, up_i), bfloat16 [M, N/2] = silu(gate)*up."""
+    require(x, BF16, "gemm_tc.x")
+    require(w, BF16, "gemm_tc.w")
+    M, K = x.shape
+    N, K2 = w.shape
+    if K != K2 or K % 8:
+        raise KernelError(f"gemm_tc: inner sizes {K} and {K2} must agree and be a multiple of 8")
+    if silu_interleaved:
+        if N % 2:
+            raise KernelError("gemm_tc: gate/up rows must come in pairs")
+        out = torch.empty((M, N // 2), dtype=BF16, device=x.device)
+    else:
+        out = torch.empty((gemm_tc_splits(M, N, K), M, N), dtype=F32, device=x.device)
+    f = fn("gemm_tc", "lumen_gemm_tc", [P, P, P, c_int, c_int, c_int, c_int, P, P])
+    check(f(ptr(x), ptr(w), ptr(out), M, N, K, 1 if silu_interleaved else 0,
+            ptr(error_flag(x.device)), stream_ptr()), "gemm_tc")
     return out
 
 

@@ -2,9 +2,15 @@
 
 "swiglu": g = y Wg^T, u = y Wu^T, z = g / (1 + exp(-g)) * u, out = z Wd^T
 (crates/aegisllm-cuda/src/executor/mlp.rs:271-356; norm_rope_kv.cu:314-325).
-Gate and up weights are stacked so that both cost one product.
+Gate and up weights are stacked so that both cost one product. For bfloat16 their rows
+are interleaved (gate_0, up_0, gate_1, up_1, ...): then a tile of the product holds both
+halves of each pair, and the tensor-core kernel applies SiLU(gate) * up in its epilogue
+and writes bfloat16 directly. With few rows the product returns float32 (partial sums)
+and the activation is applied while the down projection stages its input.
 """
 from __future__ import annotations
+
+import torch
 
 from ..ops import gemm as G
 from ..ops import kernels as K
@@ -27,15 +33,25 @@ class SwiGLU:
     def __init__(self, spec, weights, runtime):
         self.runtime = runtime
         pre = spec.prefix
-        self.gate_up = Linear.stacked([weights[f"{pre}.gate_proj.weight"],
-                                       weights[f"{pre}.up_proj.weight"]], runtime)
+        g, u = weights[f"{pre}.gate_proj.weight"], weights[f"{pre}.up_proj.weight"]
         self.down = Linear(weights[f"{pre}.down_proj.weight"], runtime)
+        self.interleaved = (not runtime.is_f32 and g.dtype == torch.bfloat16
+                            and u.dtype == torch.bfloat16)
+        if self.interleaved:
+            I, H = g.shape
+            self.gate_up = Linear(torch.stack([g, u], dim=1).reshape(2 * I, H), runtime)
+        else:
+            self.gate_up = Linear.stacked([g, u], runtime)
 
     def forward(self, y, ctx):
+        if self.interleaved and not self.down.f32:
+            z = G.gemm_gate_up_silu(y, self.gate_up.weight)         # many rows: one kernel
+            if z is not None:
+                return self.down(z, split_ok=True)
         gu = self.gate_up(y, split_ok=True)        # float32 [N, 2I], possibly S partials
         if not self.down.f32:
-            out = G.gemm_bf16_silu_gate_up(gu, self.down.weight)   # few rows: one kernel
+            out = G.gemm_down_silu(gu, self.down.weight, self.interleaved)   # few rows
             if out is not None:
                 return out
-        z = K.silu_mul(gu, self.runtime.dtype)
+        z = K.silu_mul(gu, self.runtime.dtype, interleaved=self.interleaved)
         return self.down(z, split_ok=True)

@@ -370,6 +370,50 @@ def test_gemm_small_with_silu_prologue(M, I, H):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (200, 300, 320), (2048, 1024, 4096), (1, 256, 64),
+                                    (8, 4096, 4096), (19, 311, 80), (33, 1000, 1000), (64, 6144, 1024),
+                                    (65, 130, 72), (130, 17, 1000), (16, 151936 // 4 + 8, 256)])
+def test_gemm_tc_tensor_memory_product(M, N, K_):
+    """The tcgen05 / TMA product in both orientations: sizes that end inside a tile in every
+    dimension, a k that is no multiple of the 64-wide block, one row, and the split of k."""
+    from lumenllm_b200.ops import kernels as K
+    g = gen(16)
+    x = torch.randn(M, K_, generator=g).to(BF16)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(BF16)
+    part = K.gemm_tc(dev(x), dev(w)).cpu()
+    K.check_error_flags()
+    assert part.shape == (K.gemm_tc_splits(M, N, K_), M, N)
+    ref = x.double() @ w.double().T
+    assert float((part.sum(0).double() - ref).abs().max()) < 1e-4
+    if M <= 16:        # the same row alone: same tile shape, same order of sums
+        one = K.gemm_tc(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w)).cpu()
+        assert torch.equal(one[:, 0], part[:, M // 2])
+
+
+@pytest.mark.parametrize("M,I,H", [(300, 176, 80), (2048, 1536, 256), (40, 176, 80), (3, 12288, 128)])
+def test_gemm_tc_with_silu_epilogue_on_interleaved_rows(M, I, H):
+    from lumenllm_b200.ops import kernels as K
+    g = gen(17)
+    x = torch.randn(M, H, generator=g).to(BF16)
+    wg = (torch.randn(I, H, generator=g) / math.sqrt(H)).to(BF16)
+    wu = (torch.randn(I, H, generator=g) / math.sqrt(H)).to(BF16)
+    w = torch.stack([wg, wu], dim=1).reshape(2 * I, H)
+    z = K.gemm_tc(dev(x), dev(w), silu_interleaved=True).cpu().float()
+    K.check_error_flags()
+    ref = P.swiglu(x.float() @ wg.float().T, x.float() @ wu.float().T)
+    assert z.shape == (M, I)
+    assert float(((z - ref).abs() / (1 + ref.abs())).max()) < 2 ** -7
+    # the same through the float32 product, the activation kernel and the down prologue
+    gu = K.gemm_tc(dev(x), dev(w))
+    z2 = K.silu_mul(gu, BF16, interleaved=True).cpu().float()
+    assert float(((z2 - ref).abs() / (1 + ref.abs())).max()) < 2 ** -7
+    if M <= 16:
+        wd = (torch.randn(H, I, generator=g) / math.sqrt(I)).to(BF16)
+        out = K.gemm_small(gu, dev(wd), silu_gate_up=True, interleaved=True).cpu().sum(0)
+        ref2 = ref.to(BF16).double() @ wd.double().T
+        assert float((out.double() - ref2).abs().max()) < 2e-2 * max(1.0, float(ref2.abs().max()))
+
+
 def test_argmax_ties_and_odd_vocab():
     from lumenllm_b200.ops import kernels as K
     V = 151936 + 7
