@@ -27,7 +27,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
                    int bt_stride, const int* __restrict__ seq_pos, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nq, int nkv, int window, float scale,
-                   int max_chunks, int* __restrict__ err) {
+                   int max_chunks, int* __restrict__ err, int* __restrict__ counters,
+                   __nv_bfloat16* __restrict__ out) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;
     extern __shared__ __align__(1024) unsigned char smem[];
     unsigned char* Ks = smem;                    // 2 tiles
@@ -208,6 +211,72 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             part_ml[pi * 2 + 1] = l;
         }
     }
+    if (counters == nullptr) return;   // the chunks are merged by a second kernel
+
+    // Merge without a second kernel and without waiting: every block of this (sequence, kv
+    // head) counts itself in after its partials are visible; the one that counts last merges
+    // all chunks, in rising order whoever it is, and puts the counter back to zero.
+    __shared__ int s_last;
+    __threadfence();
+    __syncthreads();
+    const int c0 = lo / AD_CHUNK, c1 = p / AD_CHUNK;
+    if (tid == 0) {
+        const int ticket = atomicAdd(&counters[b * nkv + kvh], 1);
+        s_last = (ticket == c1 - c0);
+        if (s_last) counters[b * nkv + kvh] = 0;
+    }
+    __syncthreads();
+    if (!s_last) return;
+    __threadfence();
+    // weights of the chunks first (one thread per (row, chunk)), then the sums with all loads
+    // of a thread independent of one another
+    constexpr int MAXC = 64;
+    float* s_f = reinterpret_cast<float*>(Vs);              // [G][MAXC] factors, then [G] 1/L
+    const int nch = c1 - c0 + 1;
+    if (nch <= MAXC) {
+        for (int idx = tid; idx < G * nch; idx += AD_THREADS) {
+            const int row = idx / nch, cc = idx - row * nch;
+            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks;
+            s_f[row * MAXC + cc] = __ldcg(part_ml + (base + c0 + cc) * 2);
+        }
+        __syncthreads();
+        if (tid < G) {
+            float M = -INFINITY;
+            for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, s_f[tid * MAXC + cc]);
+            const size_t base = ((size_t)b * nq + (size_t)kvh * G + tid) * max_chunks;
+            float L = 0.0f;
+            for (int cc = 0; cc < nch; ++cc) {
+                const float f = expf(s_f[tid * MAXC + cc] - M);
+                s_f[tid * MAXC + cc] = f;
+                L += __ldcg(part_ml + (base + c0 + cc) * 2 + 1) * f;
+            }
+            s_f[G * MAXC + tid] = 1.0f / L;
+        }
+        __syncthreads();
+        for (int idx = tid; idx < G * D; idx += AD_THREADS) {
+            const int row = idx / D, e = idx - row * D;
+            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks + c0;
+            float acc = 0.0f;
+#pragma unroll 4
+            for (int cc = 0; cc < nch; ++cc) acc += __ldcg(part_o + (base + cc) * D + e) * s_f[row * MAXC + cc];
+            out[((size_t)b * nq + (size_t)kvh * G + row) * D + e] =
+                __float2bfloat16_rn(acc * s_f[G * MAXC + row]);
+        }
+        return;
+    }
+    for (int idx = tid; idx < G * D; idx += AD_THREADS) {
+        const int row = idx / D, e = idx - row * D;
+        const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks;
+        float M = -INFINITY;
+        for (int cc = c0; cc <= c1; ++cc) M = fmaxf(M, __ldcg(part_ml + (base + cc) * 2));
+        float L = 0.0f, acc = 0.0f;
+        for (int cc = c0; cc <= c1; ++cc) {
+            const float f = expf(__ldcg(part_ml + (base + cc) * 2) - M);
+            L += __ldcg(part_ml + (base + cc) * 2 + 1) * f;
+            acc += __ldcg(part_o + (base + cc) * D + e) * f;
+        }
+        out[((size_t)b * nq + (size_t)kvh * G + row) * D + e] = __float2bfloat16_rn(acc * (1.0f / L));
+    }
 }
 
 // Merges the chunks of one (sequence, head) in rising order.
@@ -216,6 +285,8 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
                                            const float* __restrict__ part_ml,
                                            const int* __restrict__ seq_pos, TOut* __restrict__ out,
                                            int nq, int D, int window, int max_chunks) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     const int head = blockIdx.x, b = blockIdx.y;
     const int p = seq_pos[b];
     int lo = 0;
@@ -238,11 +309,13 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
 // Entry point. q, out: bfloat16 [B, nq, D]; caches in the swizzled layout; seq_pos[b] is the
 // position of sequence b's query (its cached length before this token). part_o and part_ml are
 // the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
+// counters: null (a second kernel merges the chunks), or B * nkv ints that are zero before the
+// call and zero again after it (the last block of each group merges).
 LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* vcache,
                                 const int* block_table, int bt_stride, const int* seq_pos,
                                 void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
                                 int d, int window, float scale, int max_chunks, int* err,
-                                cudaStream_t stream) {
+                                int* counters, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || max_chunks <= 0)
         return LUMEN_ERR_UNSUPPORTED;
@@ -256,19 +329,22 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
         const int smem = 4 * LUMEN_PAGE * 128 * 2;
         auto k = attn_decode_kernel<128>;
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        k<<<grid, AD_THREADS, smem, stream>>>(qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
-                                              nq, nkv, window, scale, max_chunks, err);
+        lumen_launch(k, dim3(grid), dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
+                                              nq, nkv, window, scale, max_chunks, err, counters,
+                                              (__nv_bfloat16*)out);
     } else if (d == 64) {
         const int smem = 4 * LUMEN_PAGE * 64 * 2;
         auto k = attn_decode_kernel<64>;
-        k<<<grid, AD_THREADS, smem, stream>>>(qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
-                                              nq, nkv, window, scale, max_chunks, err);
+        lumen_launch(k, dim3(grid), dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
+                                              nq, nkv, window, scale, max_chunks, err, counters,
+                                              (__nv_bfloat16*)out);
     } else {
         return LUMEN_ERR_UNSUPPORTED;
     }
     LUMEN_LAUNCH_CHECK();
+    if (counters != nullptr) return 0;
     dim3 cgrid(nq, B);
-    attn_decode_combine_kernel<__nv_bfloat16><<<cgrid, 128, 0, stream>>>(
+    lumen_launch(attn_decode_combine_kernel<__nv_bfloat16>, dim3(cgrid), dim3(128), 0, stream, 
         part_o, part_ml, seq_pos, (__nv_bfloat16*)out, nq, d, window, max_chunks);
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -332,5 +408,5 @@ LUMEN_API int lumen_attn_decode_noalloc(const void* q, const void* kcache, const
     float* part_o = scratch;
     float* part_ml = scratch + rows * (unsigned long long)d;
     return lumen_attn_decode(q, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml,
-                             B, nq, nkv, d, window, scale, max_chunks, err, stream);
+                             B, nq, nkv, d, window, scale, max_chunks, err, nullptr, stream);
 }

@@ -21,6 +21,8 @@ attn_generic_kernel(const T* __restrict__ q, const T* __restrict__ kcache, const
                     const int* __restrict__ tok_seq, const int* __restrict__ tok_pos,
                     T* __restrict__ out, int nq, int nkv, int d, int window, float scale,
                     int layout) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     __shared__ float qs[AG_MAX_D];
     __shared__ float ps[AG_THREADS];
     __shared__ float red[32];
@@ -90,12 +92,12 @@ LUMEN_API int lumen_attn_generic(const void* q, const void* kcache, const void* 
     if (layout == LUMEN_LAYOUT_SW128 && (!is_bf16 || d % 64 != 0)) return LUMEN_ERR_UNSUPPORTED;
     dim3 grid(N, nq);
     if (is_bf16)
-        attn_generic_kernel<__nv_bfloat16><<<grid, AG_THREADS, 0, stream>>>(
+        lumen_launch(attn_generic_kernel<__nv_bfloat16>, dim3(grid), dim3(AG_THREADS), 0, stream, 
             (const __nv_bfloat16*)q, (const __nv_bfloat16*)kcache, (const __nv_bfloat16*)vcache,
             block_table, bt_stride, tok_seq, tok_pos, (__nv_bfloat16*)out, nq, nkv, d, window, scale,
             layout);
     else
-        attn_generic_kernel<float><<<grid, AG_THREADS, 0, stream>>>(
+        lumen_launch(attn_generic_kernel<float>, dim3(grid), dim3(AG_THREADS), 0, stream, 
             (const float*)q, (const float*)kcache, (const float*)vcache, block_table, bt_stride,
             tok_seq, tok_pos, (float*)out, nq, nkv, d, window, scale, layout);
     LUMEN_LAUNCH_CHECK();

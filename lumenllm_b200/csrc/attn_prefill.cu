@@ -26,6 +26,8 @@ attn_prefill_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __
                     int bt_stride, const int* __restrict__ cu_q, const int* __restrict__ seq_start,
                     int B, __nv_bfloat16* __restrict__ out, int nq, int nkv, int window,
                     float scale_log2, int* __restrict__ err) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;
     extern __shared__ __align__(1024) unsigned char smem[];   // [2 stages][K tile, V tile]
     __shared__ uint64_t full[2];
@@ -220,12 +222,12 @@ LUMEN_API int lumen_attn_prefill(const void* q, const void* kcache, const void* 
         const int smem = 4 * LUMEN_PAGE * 128 * 2;
         auto k = attn_prefill_kernel<128>;
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        k<<<grid, AP_THREADS, smem, stream>>>(qp, kp, vp, block_table, bt_stride, cu_q, seq_start, B,
+        lumen_launch(k, dim3(grid), dim3(AP_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, cu_q, seq_start, B,
                                               (__nv_bfloat16*)out, nq, nkv, window, scale_log2, err);
     } else if (d == 64) {
         const int smem = 4 * LUMEN_PAGE * 64 * 2;
         auto k = attn_prefill_kernel<64>;
-        k<<<grid, AP_THREADS, smem, stream>>>(qp, kp, vp, block_table, bt_stride, cu_q, seq_start, B,
+        lumen_launch(k, dim3(grid), dim3(AP_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, cu_q, seq_start, B,
                                               (__nv_bfloat16*)out, nq, nkv, window, scale_log2, err);
     } else {
         return LUMEN_ERR_UNSUPPORTED;

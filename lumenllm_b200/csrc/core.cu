@@ -37,6 +37,8 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ h, int H, int V) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* out = h + (size_t)t * H;
@@ -57,9 +59,9 @@ LUMEN_API int lumen_embed(const int* tokens, const void* table, int table_is_bf1
     if (N <= 0) return 0;
     if (H <= 0 || V <= 0) return LUMEN_ERR_BAD_ARGUMENT;
     if (table_is_bf16)
-        embed_kernel<__nv_bfloat16><<<N, 256, 0, stream>>>(tokens, (const __nv_bfloat16*)table, h, H, V);
+        lumen_launch(embed_kernel<__nv_bfloat16>, dim3(N), dim3(256), 0, stream, tokens, (const __nv_bfloat16*)table, h, H, V);
     else
-        embed_kernel<float><<<N, 256, 0, stream>>>(tokens, (const float*)table, h, H, V);
+        lumen_launch(embed_kernel<float>, dim3(N), dim3(256), 0, stream, tokens, (const float*)table, h, H, V);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -69,10 +71,12 @@ LUMEN_API int lumen_embed(const int* tokens, const void* table, int table_is_bf1
 // sum is stored back to h[r]; y = x * 1/sqrt(mean(x^2)+eps) * w. With `rows`, block b reads
 // row rows[b] and writes y row b (gather of the wanted rows); without, row b.
 template <typename TOut>
-__global__ void __launch_bounds__(256)
+__global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
                    const float* __restrict__ w, float eps, TOut* __restrict__ y,
                    const int* __restrict__ rows, int H, int write_h) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     extern __shared__ __align__(16) float xs[];  // H floats
     __shared__ float red[32];
     const int b = blockIdx.x;
@@ -126,16 +130,24 @@ LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long 
     if (H <= 0 || n_delta < 0) return LUMEN_ERR_BAD_ARGUMENT;
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
+    // Few rows (decode): one row per block cannot fill the GPU, so each block is made wide and
+    // every thread has all its loads in flight at once. Many rows: 256 threads a row.
+    int threads = 256;
+    if (n_rows < 2 * 148) {
+        threads = ((H / 4 + 31) / 32) * 32;
+        if (threads > 1024) threads = 1024;
+        if (threads < 128) threads = 128;
+    }
     if (y_is_bf16) {
         auto k = add_rmsnorm_kernel<__nv_bfloat16>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<n_rows, 256, smem, stream>>>(h, delta, n_delta, (size_t)delta_stride, w, eps,
-                                         (__nv_bfloat16*)y, rows, H, write_h);
+        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, n_delta, (size_t)delta_stride, w, eps,
+                                             (__nv_bfloat16*)y, rows, H, write_h);
     } else {
         auto k = add_rmsnorm_kernel<float>;
         if (smem > 48 * 1024) cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        k<<<n_rows, 256, smem, stream>>>(h, delta, n_delta, (size_t)delta_stride, w, eps, (float*)y,
-                                         rows, H, write_h);
+        lumen_launch(k, dim3(n_rows), dim3(threads), smem, stream, h, delta, n_delta, (size_t)delta_stride, w, eps, (float*)y,
+                                             rows, H, write_h);
     }
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -147,6 +159,8 @@ LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long 
 template <typename TOut>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int S, size_t split_stride,
                                 TOut* __restrict__ z, long long total, int I, int interleaved) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long step = (long long)gridDim.x * blockDim.x;
     if (interleaved) {
@@ -201,10 +215,10 @@ LUMEN_API int lumen_silu_mul(const float* gu, int n_splits, void* z, int z_is_bf
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
     if (z_is_bf16)
-        silu_mul_kernel<__nv_bfloat16><<<(int)blocks, 256, 0, stream>>>(gu, n_splits, stride,
+        lumen_launch(silu_mul_kernel<__nv_bfloat16>, dim3((int)blocks), dim3(256), 0, stream, gu, n_splits, stride,
                                                                        (__nv_bfloat16*)z, total, I, interleaved);
     else
-        silu_mul_kernel<float><<<(int)blocks, 256, 0, stream>>>(gu, n_splits, stride, (float*)z, total, I,
+        lumen_launch(silu_mul_kernel<float>, dim3((int)blocks), dim3(256), 0, stream, gu, n_splits, stride, (float*)z, total, I,
                                                                 interleaved);
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -215,6 +229,8 @@ LUMEN_API int lumen_silu_mul(const float* gu, int n_splits, void* z, int z_is_bf
 // and read by every layer that shares the position encoding.
 __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
                                   float2* __restrict__ cs, int N, int half) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)N * half) return;
     const int n = (int)(idx / half), i = (int)(idx - (long long)n * half);
@@ -228,7 +244,7 @@ LUMEN_API int lumen_rope_table(const int* pos, const float* inv_freq, float* cs,
                                cudaStream_t stream) {
     if (N <= 0 || half <= 0) return 0;
     const long long total = (long long)N * half;
-    rope_table_kernel<<<(int)((total + 255) / 256), 256, 0, stream>>>(pos, inv_freq, (float2*)cs, N, half);
+    lumen_launch(rope_table_kernel, dim3((int)((total + 255) / 256)), dim3(256), 0, stream, pos, inv_freq, (float2*)cs, N, half);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -250,6 +266,8 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, int S, 
                                           const int* __restrict__ block_table, int bt_stride,
                                           T* __restrict__ q_out, T* __restrict__ kcache,
                                           T* __restrict__ vcache, int nq, int nkv, int d, int layout) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     extern __shared__ __align__(16) float rowbuf[];  // [warps][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x;
@@ -304,6 +322,68 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, int S, 
     }
 }
 
+// The same for head size 128 rotated over all 128 values: a lane keeps 4 consecutive values
+// in registers, the partner of value e in the rotation (e +- 64) lives 16 lanes away, and
+// nothing goes through shared memory.
+template <typename T>
+__global__ void __launch_bounds__(256)
+qk_norm_rope_store_d128_kernel(const float* __restrict__ qkv, int S, size_t split_stride,
+                               const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                               const float2* __restrict__ cs, int rot, const int* __restrict__ cache_pos,
+                               const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                               int bt_stride, T* __restrict__ q_out, T* __restrict__ kcache,
+                               T* __restrict__ vcache, int nq, int nkv, int layout) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
+    constexpr int d = 128;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n = blockIdx.x;
+    const int head = blockIdx.y * 8 + warp;
+    const int nheads = nq + 2 * nkv;
+    if (head >= nheads) return;
+    const float* src = qkv + ((size_t)n * nheads + head) * d + 4 * lane;
+    float4 v = load4(src);
+    for (int s = 1; s < S; ++s) {
+        const float4 v2 = load4(src + s * split_stride);
+        v.x += v2.x; v.y += v2.y; v.z += v2.z; v.w += v2.w;
+    }
+    const bool is_q = head < nq;
+    const bool is_k = !is_q && head < nq + nkv;
+    const float* nw = is_q ? qw : (is_k ? kw : nullptr);
+    if (nw) {
+        float ss = v.x * v.x;
+        ss += v.y * v.y;
+        ss += v.z * v.z;
+        ss += v.w * v.w;
+        ss = warp_sum(ss);
+        const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+        const float4 g = load4(nw + 4 * lane);
+        v.x = v.x * scale * g.x; v.y = v.y * scale * g.y; v.z = v.z * scale * g.z; v.w = v.w * scale * g.w;
+    }
+    if ((is_q || is_k) && rot == d) {
+        const float4 o = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 16), __shfl_xor_sync(0xffffffffu, v.y, 16),
+                                     __shfl_xor_sync(0xffffffffu, v.z, 16), __shfl_xor_sync(0xffffffffu, v.w, 16));
+        const float4* csn = reinterpret_cast<const float4*>(cs + (size_t)n * 64 + 4 * (lane & 15));
+        const float4 c01 = csn[0], c23 = csn[1];     // (cos, sin) of 4 consecutive pairs
+        if (lane < 16) {     // x'_i = x_i cos - x_{i+64} sin
+            v.x = v.x * c01.x - o.x * c01.y; v.y = v.y * c01.z - o.y * c01.w;
+            v.z = v.z * c23.x - o.z * c23.y; v.w = v.w * c23.z - o.w * c23.w;
+        } else {             // x'_{i+64} = x_i sin + x_{i+64} cos
+            v.x = o.x * c01.y + v.x * c01.x; v.y = o.y * c01.w + v.y * c01.z;
+            v.z = o.z * c23.y + v.z * c23.x; v.w = o.w * c23.w + v.w * c23.z;
+        }
+    }
+    if (is_q) {
+        Pack4<T>::store(q_out + ((size_t)n * nq + head) * d + 4 * lane, v.x, v.y, v.z, v.w);
+    } else {
+        const int kvh = is_k ? head - nq : head - nq - nkv;
+        const int cp = cache_pos[n];
+        const int page = block_table[(size_t)tok_seq[n] * bt_stride + cp / LUMEN_PAGE];
+        T* tile = (is_k ? kcache : vcache) + ((size_t)page * nkv + kvh) * LUMEN_PAGE * d;
+        Pack4<T>::store(tile + tile_offset(layout, cp % LUMEN_PAGE, 4 * lane, d), v.x, v.y, v.z, v.w);
+    }
+}
+
 LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, int n_splits, const float* qw, const float* kw,
                                        float eps, const float* cs, int rot, const int* cache_pos,
                                        const int* tok_seq, const int* block_table, int bt_stride,
@@ -319,16 +399,31 @@ LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, int n_splits, const flo
     const int nheads = nq + 2 * nkv;
     if (nheads == 0) return 0;
     if ((nheads + warps - 1) / warps > 65535) return LUMEN_ERR_UNSUPPORTED;
+    if (d == 128 && (rot == 128 || rot == 0)) {
+        dim3 g8(N, (nheads + 7) / 8);
+        const size_t st = (size_t)N * nheads * d;
+        if (is_bf16)
+            lumen_launch(qk_norm_rope_store_d128_kernel<__nv_bfloat16>, dim3(g8), dim3(256), 0, stream, 
+                qkv, n_splits, st, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
+                bt_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nq, nkv,
+                layout);
+        else
+            lumen_launch(qk_norm_rope_store_d128_kernel<float>, dim3(g8), dim3(256), 0, stream, 
+                qkv, n_splits, st, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
+                bt_stride, (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, layout);
+        LUMEN_LAUNCH_CHECK();
+        return 0;
+    }
     dim3 grid(N, (nheads + warps - 1) / warps);
     const size_t smem = (size_t)warps * d * sizeof(float);
     const size_t stride = (size_t)N * nheads * d;
     if (is_bf16)
-        qk_norm_rope_store_kernel<__nv_bfloat16><<<grid, warps * 32, smem, stream>>>(
+        lumen_launch(qk_norm_rope_store_kernel<__nv_bfloat16>, dim3(grid), dim3(warps * 32), smem, stream, 
             qkv, n_splits, stride, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
             bt_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nq, nkv, d,
             layout);
     else
-        qk_norm_rope_store_kernel<float><<<grid, warps * 32, smem, stream>>>(
+        lumen_launch(qk_norm_rope_store_kernel<float>, dim3(grid), dim3(warps * 32), smem, stream, 
             qkv, n_splits, stride, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
             bt_stride, (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, d, layout);
     LUMEN_LAUNCH_CHECK();

@@ -13,6 +13,8 @@ template <typename TW>
 __global__ void __launch_bounds__(256)
 gemm_f32_kernel(const float* __restrict__ A, const TW* __restrict__ W, float* __restrict__ C, int M,
                 int N, int K) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     __shared__ float As[BK][BM + 4];
     __shared__ float Ws[BK][BN + 4];
     const int tx = threadIdx.x & 15, ty = threadIdx.x >> 4;
@@ -67,9 +69,9 @@ LUMEN_API int lumen_gemm_f32(const float* A, const void* W, int w_is_bf16, float
     dim3 grid((N + BN - 1) / BN, (M + BM - 1) / BM);
     if (grid.y > 65535) return LUMEN_ERR_UNSUPPORTED;
     if (w_is_bf16)
-        gemm_f32_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(A, (const __nv_bfloat16*)W, C, M, N, K);
+        lumen_launch(gemm_f32_kernel<__nv_bfloat16>, dim3(grid), dim3(256), 0, stream, A, (const __nv_bfloat16*)W, C, M, N, K);
     else
-        gemm_f32_kernel<float><<<grid, 256, 0, stream>>>(A, (const float*)W, C, M, N, K);
+        lumen_launch(gemm_f32_kernel<float>, dim3(grid), dim3(256), 0, stream, A, (const float*)W, C, M, N, K);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

@@ -103,6 +103,35 @@ gemm_small_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ 
     const int kpad = (klen + 63) & ~63;
     const int xstride = kpad + 32;                 // +64 bytes: rows 16 banks apart, no conflicts
     constexpr int MP = 8 * NT;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n0 = blockIdx.x * GS_ROWS + warp * 16;
+    const int r0 = n0 + g, r1 = n0 + g + 8;
+    const bool ok0 = r0 < N, ok1 = r1 < N;
+    const __nv_bfloat16* w0 = W + (size_t)(ok0 ? r0 : 0) * K + k0 + 8 * t;
+    const __nv_bfloat16* w1 = W + (size_t)(ok1 ? r1 : 0) * K + k0 + 8 * t;
+    const int nchunks = kpad >> 6;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+    uint4 a[GS_UNROLL][4];
+    // a chunk's two halves: k in [kc + 8t, +8) and [kc + 32 + 8t, +8)
+    auto load_group = [&](int cb) {
+#pragma unroll
+        for (int u = 0; u < GS_UNROLL; ++u) {
+            const int kc = (cb + u) << 6;
+            const bool in_lo = (cb + u) < nchunks && kc + 8 * t + 8 <= klen;
+            const bool in_hi = (cb + u) < nchunks && kc + 32 + 8 * t + 8 <= klen;
+            a[u][0] = (ok0 && in_lo) ? ldg_stream(w0 + kc) : zero;
+            a[u][1] = (ok1 && in_lo) ? ldg_stream(w1 + kc) : zero;
+            a[u][2] = (ok0 && in_hi) ? ldg_stream(w0 + kc + 32) : zero;
+            a[u][3] = (ok1 && in_hi) ? ldg_stream(w1 + kc + 32) : zero;
+        }
+    };
+    // Weights never change: the first loads are on their way before the kernel ahead of this
+    // one in the stream has finished. Activations and outputs come after the wait.
+    load_group(0);
+    pdl_wait();
+    pdl_trigger();
+
     // zero the padding of the last chunk, then stage
     if (kpad != klen)
         for (int idx = threadIdx.x; idx < MP * (kpad - klen); idx += GS_THREADS) {
@@ -111,35 +140,13 @@ gemm_small_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ 
         }
     stage_x<MODE>(x, XS, xs, M, MP, K, k0, klen, xstride);
     __syncthreads();
-
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int g = lane >> 2, t = lane & 3;
-    const int n0 = blockIdx.x * GS_ROWS + warp * 16;
     if (n0 >= N) return;
-    const int r0 = n0 + g, r1 = n0 + g + 8;
-    const bool ok0 = r0 < N, ok1 = r1 < N;
-    const __nv_bfloat16* w0 = W + (size_t)(ok0 ? r0 : 0) * K + k0 + 8 * t;
-    const __nv_bfloat16* w1 = W + (size_t)(ok1 ? r1 : 0) * K + k0 + 8 * t;
 
     float c[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
-
-    const int nchunks = kpad >> 6;
-    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
     for (int cb = 0; cb < nchunks; cb += GS_UNROLL) {
-        uint4 a[GS_UNROLL][4];
-#pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
-            const int kc = (cb + u) << 6;
-            // a chunk's two halves: k in [kc + 8t, +8) and [kc + 32 + 8t, +8)
-            const bool in_lo = (cb + u) < nchunks && kc + 8 * t + 8 <= klen;
-            const bool in_hi = (cb + u) < nchunks && kc + 32 + 8 * t + 8 <= klen;
-            a[u][0] = (ok0 && in_lo) ? ldg_stream(w0 + kc) : zero;
-            a[u][1] = (ok1 && in_lo) ? ldg_stream(w1 + kc) : zero;
-            a[u][2] = (ok0 && in_hi) ? ldg_stream(w0 + kc + 32) : zero;
-            a[u][3] = (ok1 && in_hi) ? ldg_stream(w1 + kc + 32) : zero;
-        }
+        if (cb > 0) load_group(cb);
 #pragma unroll
         for (int u = 0; u < GS_UNROLL; ++u) {
             if (cb + u >= nchunks) break;
@@ -209,7 +216,7 @@ LUMEN_API int lumen_gemm_small(const void* x, int mode, int x_splits, const void
         auto k = gemm_small_kernel<NT_, MODE_>;                                                    \
         if (smem > 48 * 1024)                                                                      \
             cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        k<<<grid, GS_THREADS, smem, stream>>>(x, Wp, out, M, N, K, slice, x_splits);               \
+        lumen_launch(k, dim3(grid), dim3(GS_THREADS), smem, stream, x, Wp, out, M, N, K, slice, x_splits);               \
     } while (0)
     if (NT == 1 && mode == 0) GS_LAUNCH(1, 0);
     else if (NT == 1 && mode == 1) GS_LAUNCH(1, 1);

@@ -137,6 +137,13 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     __syncthreads();
     tc_fence_after();
     const uint32_t tmem_base = *tmem_slot;
+    // Set-up above depends on nothing. From here on every role waits for the kernels ahead
+    // of this one before it touches activations or outputs; the producer first requests
+    // weights (below).
+    if (warp != 0) {
+        pdl_wait();
+        pdl_trigger();
+    }
 
     // item -> (tile of A, tile of B, split); tiles of A vary fastest so that blocks working at
     // the same time share their B tile through L2
@@ -149,19 +156,49 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 
     if (warp == 0) {
         if (lane == 0) {
-            int it = 0;
-            for (int item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x) {
-                int ta, tb, s;
+            // the sequence of (tile of A, tile of B, k block) this block works through
+            int item = blockIdx.x, ta = 0, tb = 0, s = 0, kb = 0, kb1 = 0;
+            bool have = item < n_items;
+            auto enter = [&]() {
                 decode(item, ta, tb, s);
-                const int kb0 = s * p.kb_per_split, kb1 = min(kb0 + p.kb_per_split, p.num_kb);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int st = it % STAGES, ph = (it / STAGES) & 1;
-                    if (!mbar_wait(&empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
-                    mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
-                    tma_load_2d(sA + st * A_BYTES, &tmA, kb * TC_BK, ta * TC_BM, &full[st]);
-                    tma_load_2d(sB + st * B_BYTES, &tmB, kb * TC_BK, tb * BN, &full[st]);
+                kb = s * p.kb_per_split;
+                kb1 = min(kb + p.kb_per_split, p.num_kb);
+            };
+            auto advance = [&]() {
+                if (++kb >= kb1) {
+                    item += gridDim.x;
+                    have = item < n_items;
+                    if (have) enter();
                 }
+            };
+            if (have) enter();
+            // Weights never change, so the first ring of weight tiles is requested before the
+            // kernel ahead of this one in the stream has finished; activations only after.
+            int npre = 0, pt[STAGES], pk[STAGES];
+            while (have && npre < STAGES) {
+                pt[npre] = SWAP ? tb : ta;
+                pk[npre] = kb;
+                mbar_expect_tx(&full[npre], A_BYTES + B_BYTES);
+                if (SWAP) tma_load_2d(sA + npre * A_BYTES, &tmA, kb * TC_BK, ta * TC_BM, &full[npre]);
+                else      tma_load_2d(sB + npre * B_BYTES, &tmB, kb * TC_BK, tb * BN, &full[npre]);
+                ++npre;
+                advance();
             }
+            pdl_wait();
+            pdl_trigger();
+            for (int i = 0; i < npre; ++i) {
+                if (SWAP) tma_load_2d(sB + i * B_BYTES, &tmB, pk[i] * TC_BK, pt[i] * BN, &full[i]);
+                else      tma_load_2d(sA + i * A_BYTES, &tmA, pk[i] * TC_BK, pt[i] * TC_BM, &full[i]);
+            }
+            for (int it = npre; have && !*abort_flag; ++it, advance()) {
+                const int st = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait(&empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
+                mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
+                tma_load_2d(sA + st * A_BYTES, &tmA, kb * TC_BK, ta * TC_BM, &full[st]);
+                tma_load_2d(sB + st * B_BYTES, &tmB, kb * TC_BK, tb * BN, &full[st]);
+            }
+        } else {
+            pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0) {
@@ -330,6 +367,7 @@ LUMEN_API int lumen_gemm_tc_splits(int M, int N, int K, int epi) {
     const int num_kb = (K + TC_BK - 1) / TC_BK;
     const int tiles = (N + TC_BM - 1) / TC_BM;
     const int sms = 148;   // fixed, so that the split never depends on the device at hand
+    if (tiles >= 4 * sms) return 1;             // enough tiles: a split would only add traffic
     int best = 1;
     double best_eff = 0.0;
     for (int s = 1; s <= 16 && s <= num_kb; ++s) {
@@ -355,7 +393,7 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     const int tilesA = (p.rowsA + TC_BM - 1) / TC_BM, tilesB = (p.rowsB + BN - 1) / BN;
     const int items = tilesA * tilesB * p.splits;
     const int grid = items < sm_count() ? items : sm_count();
-    k<<<grid, TC_THREADS, smem, stream>>>(ma, mb, p);
+    lumen_launch(k, dim3(grid), dim3(TC_THREADS), smem, stream, ma, mb, p);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

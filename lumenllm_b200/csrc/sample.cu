@@ -217,6 +217,8 @@ __device__ void block_argmax(const float* lg, int V, float* out_v, int* out_i, S
 
 __global__ void __launch_bounds__(SM_THREADS)
 argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int* __restrict__ out) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     __shared__ Shared sh;
     float v;
     int i;
@@ -224,11 +226,70 @@ argmax_kernel(const float* __restrict__ logits, long long row_stride, int V, int
     if (threadIdx.x == 0) out[blockIdx.x] = i;
 }
 
+// Two-stage argmax for long rows: AM_SLICES blocks per row each reduce a slice, a small
+// second kernel reduces the slices in rising order (so equal maxima still resolve to the
+// lowest index).
+#define AM_SLICES 64
+__global__ void __launch_bounds__(256)
+argmax_slices_kernel(const float* __restrict__ logits, long long row_stride, int V,
+                     float* __restrict__ part_v, int* __restrict__ part_i) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
+    __shared__ float sv[8];
+    __shared__ int si[8];
+    const int row = blockIdx.y, slice = blockIdx.x;
+    const float* lg = logits + (size_t)row * row_stride;
+    const int per = (V + AM_SLICES - 1) / AM_SLICES;
+    const int beg = slice * per, end = min(beg + per, V);
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int i = beg + threadIdx.x; i < end; i += blockDim.x) {
+        const float x = lg[i];
+        if (x > bv || (x == bv && i < bi)) { bv = x; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if ((threadIdx.x & 31) == 0) { sv[threadIdx.x >> 5] = bv; si[threadIdx.x >> 5] = bi; }
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        for (int w = 1; w < 8; ++w)
+            if (sv[w] > bv || (sv[w] == bv && si[w] < bi)) { bv = sv[w]; bi = si[w]; }
+        part_v[row * AM_SLICES + slice] = bv;
+        part_i[row * AM_SLICES + slice] = bi;
+    }
+}
+__global__ void argmax_final_kernel(const float* __restrict__ part_v, const int* __restrict__ part_i,
+                                    int* __restrict__ out) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
+    const int row = blockIdx.x, lane = threadIdx.x;   // 32 threads
+    float bv = -INFINITY;
+    int bi = 0x7fffffff;
+    for (int s = lane; s < AM_SLICES; s += 32) {
+        const float v = part_v[row * AM_SLICES + s];
+        const int i = part_i[row * AM_SLICES + s];
+        if (v > bv || (v == bv && i < bi)) { bv = v; bi = i; }
+    }
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        const float ov = __shfl_xor_sync(0xffffffffu, bv, o);
+        const int oi = __shfl_xor_sync(0xffffffffu, bi, o);
+        if (ov > bv || (ov == bv && oi < bi)) { bv = ov; bi = oi; }
+    }
+    if (lane == 0) out[row] = (bi == 0x7fffffff) ? 0 : bi;
+}
+
 // opts: per row (temperature, top_p, min_p, u); top_k: per row.
 __global__ void __launch_bounds__(SM_THREADS)
 sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
               const float* __restrict__ opts, const int* __restrict__ top_k_arr,
               int* __restrict__ out) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
     __shared__ Shared sh;
     const float* lg = logits + (size_t)blockIdx.x * row_stride;
     const float temperature = opts[blockIdx.x * 4 + 0];
@@ -333,11 +394,20 @@ sample_kernel(const float* __restrict__ logits, long long row_stride, int V,
     if (threadIdx.x == 0) out[blockIdx.x] = result;
 }
 
+// scratch: optional, 2 * 64 * B 4-byte words; with it long rows are reduced by many blocks.
 LUMEN_API int lumen_argmax(const float* logits, long long row_stride, int B, int V, int* out,
-                           cudaStream_t stream) {
+                           void* scratch, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return LUMEN_ERR_BAD_ARGUMENT;
-    argmax_kernel<<<B, SM_THREADS, 0, stream>>>(logits, row_stride, V, out);
+    if (scratch && V >= 16384 && B <= 65535) {
+        float* pv = (float*)scratch;
+        int* pi = (int*)scratch + (size_t)B * AM_SLICES;
+        lumen_launch(argmax_slices_kernel, dim3(dim3(AM_SLICES, B)), dim3(256), 0, stream, logits, row_stride, V, pv, pi);
+        LUMEN_LAUNCH_CHECK();
+        lumen_launch(argmax_final_kernel, dim3(B), dim3(32), 0, stream, pv, pi, out);
+    } else {
+        lumen_launch(argmax_kernel, dim3(B), dim3(SM_THREADS), 0, stream, logits, row_stride, V, out);
+    }
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -346,7 +416,7 @@ LUMEN_API int lumen_sample(const float* logits, long long row_stride, int B, int
                            const float* opts, const int* top_k, int* out, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (V <= 0) return LUMEN_ERR_BAD_ARGUMENT;
-    sample_kernel<<<B, SM_THREADS, 0, stream>>>(logits, row_stride, V, opts, top_k, out);
+    lumen_launch(sample_kernel, dim3(B), dim3(SM_THREADS), 0, stream, logits, row_stride, V, opts, top_k, out);
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

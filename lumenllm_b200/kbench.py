@@ -1,0 +1,124 @@
+"""Micro-benchmarks of single kernels at chosen sizes:
+
+    python -m lumenllm_b200.kbench gemm_tc --m 2048 --n 4096 --k 4096 [--silu] [--copies 8] [--reps 5]
+    python -m lumenllm_b200.kbench gemm_small --m 8 --n 4096 --k 4096
+    python -m lumenllm_b200.kbench attn_decode --batch 8 --len 1600 --heads 32 --kv-heads 8 --head-dim 128
+    python -m lumenllm_b200.kbench attn_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
+    python -m lumenllm_b200.kbench add_rmsnorm --m 2048 --n 4096
+    python -m lumenllm_b200.kbench qk_rope --m 2048 --heads 32 --kv-heads 8 --head-dim 128
+
+Each run cycles through `--copies` distinct operand sets (more bytes than the L2 holds, so
+that what is timed comes from HBM), times `--reps` passes with CUDA events after a warm-up and
+prints one line: microseconds per launch, and GB/s of the bytes the kernel has to move or
+TFLOP/s of its products. It is also the small workload that profiler captures are taken on.
+"""
+from __future__ import annotations
+
+import argparse
+import math
+
+import torch
+
+from .ops import kernels as K
+
+
+def _time(fns, reps):
+    for f in fns:
+        f()
+    torch.cuda.synchronize()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    e0.record()
+    for _ in range(reps):
+        for f in fns:
+            f()
+    e1.record()
+    torch.cuda.synchronize()
+    return e0.elapsed_time(e1) * 1000.0 / (reps * len(fns))
+
+
+def _paged(B, length, nkv, d, dev):
+    pages = (length + 63) // 64
+    n_pages = B * pages + 1
+    kc = torch.randn(n_pages, nkv, 64, d, device=dev).to(torch.bfloat16)
+    vc = torch.randn(n_pages, nkv, 64, d, device=dev).to(torch.bfloat16)
+    table = (torch.arange(B * pages, device=dev, dtype=torch.int32) + 1).view(B, pages)
+    return kc, vc, table
+
+
+def main(argv=None):
+    ap = argparse.ArgumentParser(prog="kbench")
+    ap.add_argument("kernel", choices=["gemm_tc", "gemm_small", "attn_decode", "attn_prefill",
+                                       "add_rmsnorm", "qk_rope"])
+    ap.add_argument("--m", type=int, default=2048)
+    ap.add_argument("--n", type=int, default=4096)
+    ap.add_argument("--k", type=int, default=4096)
+    ap.add_argument("--silu", action="store_true")
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--len", type=int, default=1600)
+    ap.add_argument("--tokens", type=int, default=2048)
+    ap.add_argument("--heads", type=int, default=32)
+    ap.add_argument("--kv-heads", type=int, default=8)
+    ap.add_argument("--head-dim", type=int, default=128)
+    ap.add_argument("--copies", type=int, default=8)
+    ap.add_argument("--reps", type=int, default=5)
+    a = ap.parse_args(argv)
+    dev = torch.device("cuda", 0)
+    torch.manual_seed(0)
+    bf = torch.bfloat16
+    note = ""
+    if a.kernel in ("gemm_tc", "gemm_small"):
+        ws = [(torch.randn(a.n, a.k, device=dev) / math.sqrt(a.k)).to(bf) for _ in range(a.copies)]
+        x = torch.randn(a.m, a.k, device=dev).to(bf)
+        if a.kernel == "gemm_tc":
+            fns = [lambda w=w: K.gemm_tc(x, w, silu_interleaved=a.silu) for w in ws]
+        else:
+            fns = [lambda w=w: K.gemm_small(x, w) for w in ws]
+        us = _time(fns, a.reps)
+        nbytes = a.n * a.k * 2 + a.m * a.k * 2
+        flops = 2.0 * a.m * a.n * a.k
+        note = f"{nbytes / us / 1e3:.0f} GB/s  {flops / us / 1e6:.1f} TFLOP/s"
+    elif a.kernel == "attn_decode":
+        sets = [_paged(a.batch, a.len, a.kv_heads, a.head_dim, dev) for _ in range(a.copies)]
+        q = torch.randn(a.batch, a.heads, a.head_dim, device=dev).to(bf)
+        pos = torch.full((a.batch,), a.len - 1, dtype=torch.int32, device=dev)
+        fns = [lambda s=s: K.attn_decode(q, s[0], s[1], s[2], pos, 0, a.head_dim ** -0.5) for s in sets]
+        us = _time(fns, a.reps)
+        nbytes = 2 * a.batch * a.len * a.kv_heads * a.head_dim * 2
+        note = f"{nbytes / us / 1e3:.0f} GB/s"
+    elif a.kernel == "attn_prefill":
+        kc, vc, table = _paged(1, a.tokens, a.kv_heads, a.head_dim, dev)
+        q = torch.randn(a.tokens, a.heads, a.head_dim, device=dev).to(bf)
+        cu = torch.tensor([0, a.tokens], dtype=torch.int32, device=dev)
+        st = torch.zeros(1, dtype=torch.int32, device=dev)
+        fns = [lambda: K.attn_prefill(q, kc, vc, table, cu, st, [a.tokens], 0, a.head_dim ** -0.5)]
+        us = _time(fns, a.reps)
+        flops = 2.0 * a.tokens * a.tokens * a.head_dim * a.heads      # causal: half of 4 T^2 d
+        note = f"{flops / us / 1e6:.1f} TFLOP/s"
+    elif a.kernel == "add_rmsnorm":
+        hs = [torch.randn(a.m, a.n, device=dev) for _ in range(a.copies)]
+        ds = [torch.randn(1, a.m, a.n, device=dev) for _ in range(a.copies)]
+        w = torch.ones(a.n, device=dev)
+        fns = [lambda h=h, d=d: K.add_rmsnorm(h, d, w, 1e-6, bf) for h, d in zip(hs, ds)]
+        us = _time(fns, a.reps)
+        note = f"{a.m * a.n * 14 / us / 1e3:.0f} GB/s"
+    else:
+        nh = a.heads + 2 * a.kv_heads
+        xs = [torch.randn(a.m, nh * a.head_dim, device=dev) for _ in range(a.copies)]
+        kc, vc, table = _paged(1, a.m, a.kv_heads, a.head_dim, dev)
+        pos = torch.arange(a.m, dtype=torch.int32, device=dev)
+        seq = torch.zeros(a.m, dtype=torch.int32, device=dev)
+        inv = 1.0 / (1e6 ** (torch.arange(0, a.head_dim, 2, dtype=torch.float32) / a.head_dim))
+        cs = K.rope_table(pos, inv.to(dev))
+        wn = torch.ones(a.head_dim, device=dev)
+        fns = [lambda x=x: K.qk_norm_rope_store(x, wn, wn, 1e-6, cs, a.head_dim, pos, seq, table, kc, vc,
+                                                a.heads, a.kv_heads, a.head_dim, bf, layout=K.LAYOUT_SW128)
+               for x in xs]
+        us = _time(fns, a.reps)
+        note = f"{a.m * nh * a.head_dim * 6 / us / 1e3:.0f} GB/s"
+    K.check_error_flags()
+    print(f"{a.kernel}: {us:.1f} us per launch  {note}")
+    return 0
+
+
+if __name__ == "__main__":
+    raise SystemExit(main())

@@ -19,11 +19,12 @@ torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
 
-SMALL_MAX_N = 8192      # tallest weight the register-streaming kernel is preferred for
+SMALL_MAX_N = 8192      # tallest and widest weight the register-streaming kernel is preferred for
+SMALL_MAX_K = 8192
 
 
 def takes_small(M: int, Kdim: int, N: int) -> bool:
-    return M <= K.SMALL_M and Kdim % 8 == 0 and N <= SMALL_MAX_N
+    return M <= K.SMALL_M and Kdim % 8 == 0 and N <= SMALL_MAX_N and Kdim <= SMALL_MAX_K
 
 
 def takes_tc(x: torch.Tensor, w: torch.Tensor) -> bool:

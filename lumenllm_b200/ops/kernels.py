@@ -255,8 +255,9 @@ def argmax(logits, out=None):
         raise KernelError("argmax: rows must be contiguous")
     if out is None:
         out = torch.empty((B,), dtype=I32, device=logits.device)
-    f = fn("sample", "lumen_argmax", [P, c_longlong, c_int, c_int, P, P])
-    check(f(ptr(logits), logits.stride(0), B, V, ptr(out), stream_ptr()), "argmax")
+    scratch = torch.empty((2 * 64 * B,), dtype=I32, device=logits.device) if V >= 16384 else None
+    f = fn("sample", "lumen_argmax", [P, c_longlong, c_int, c_int, P, P, P])
+    check(f(ptr(logits), logits.stride(0), B, V, ptr(out), ptr(scratch), stream_ptr()), "argmax")
     return out
 
 
@@ -296,6 +297,20 @@ def check_error_flags() -> None:
             raise KernelError(f"a kernel on cuda:{dev} gave up waiting for its own copies")
 
 
+_COUNTERS = 1 << 16
+_counters = {}
+
+
+def _decode_counters(device) -> torch.Tensor:
+    """Zeroed ints that the decode-attention blocks count themselves in with; every call
+    leaves them zero again, and calls on a device run in stream order."""
+    key = torch.device(device).index
+    t = _counters.get(key)
+    if t is None:
+        t = _counters[key] = torch.zeros((_COUNTERS,), dtype=I32, device=device)
+    return t
+
+
 def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     """Split-KV decode attention, bfloat16, swizzled cache, head size 64 or 128, at most
     16 query heads per kv head. q [B, nq, d]; seq_pos int32 [B]: each query's position."""
@@ -313,11 +328,12 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     out = torch.empty_like(q)
     part_o = torch.empty((B, nq, max_chunks, d), dtype=F32, device=q.device)
     part_ml = torch.empty((B, nq, max_chunks, 2), dtype=F32, device=q.device)
+    counters = _decode_counters(q.device) if B * nkv <= _COUNTERS else None
     f = fn("attn_decode", "lumen_attn_decode",
-           [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P])
+           [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(seq_pos),
             ptr(out), ptr(part_o), ptr(part_ml), B, nq, nkv, d, int(window), float(scale), max_chunks,
-            ptr(error_flag(q.device)), stream_ptr()), "attn_decode")
+            ptr(error_flag(q.device)), ptr(counters), stream_ptr()), "attn_decode")
     return out
 
 
