@@ -1,25 +1,29 @@
 // Decode attention over the paged cache for bfloat16, split over the keys.
 //
-// One query token per sequence. A block takes one chunk of 128 keys (two pages) of
-// one kv head of one sequence and serves all query heads of that kv head at once,
-// so every key and value is read from HBM exactly once per step. The two K tiles and
-// two V tiles of the chunk are staged by four bulk asynchronous copies
-// (cp.async.bulk, completion on an mbarrier): a page tile is contiguous and already
-// in the 128-byte-swizzled layout, so no tensor map and no address arithmetic per
-// element is needed. Each of the four warps then owns 32 keys: S = Q K^T and
-// O = P V run on the tensor cores (mma.sync m16n8k16, the query heads of the group
-// padded to 16 rows; the kernel is bound by HBM, the padding costs nothing), softmax
-// in float32. The block merges its four warps and writes one partial (unnormalised
-// O, running max m, sum l) per (sequence, head, chunk); a second kernel merges the
-// chunks in rising order. Chunk edges are multiples of 128 in absolute position, so
-// the result for a token does not depend on its neighbours in the batch.
+// One query token per sequence. A block takes one SEGMENT of a sequence (8 pages = 512 keys)
+// for one kv head and serves all query heads of that kv head at once, so every key and value
+// is read from HBM exactly once per step. The block walks its pages through a three-stage
+// ring: the K tile and the V tile of a page are each one contiguous, already swizzled block
+// of the cache and are brought in by one bulk asynchronous copy each (cp.async.bulk,
+// completion on an mbarrier), while the tensor cores work on the page before: no tensor
+// map, no address arithmetic per element. Each of the four warps owns 16 keys of a page:
+// S = Q K^T and O = P V run as mma.sync m16n8k16 with the query heads of the group padded to
+// 16 rows (the kernel is bound by HBM; the padding costs nothing), softmax online in
+// float32 per warp across the pages. At the end the block merges its four warps. A sequence
+// that fits one segment is finished there; otherwise the block writes one partial
+// (unnormalised O, running max m, sum l) per (sequence, head, segment) and the segments are
+// merged in rising order, either by the block of the group that finishes last (it learns
+// that from a counter; nobody waits) or by a second kernel. Segment and page edges are
+// multiples of 512 and 64 in absolute position, so the result for a token does not depend
+// on its neighbours in the batch.
 //
-// Scratch: part_o [B, nq, max_chunks, D] and part_ml [B, nq, max_chunks, 2] float32.
+// Scratch: part_o [B, nq, max_segs, D] and part_ml [B, nq, max_segs, 2] float32.
 #include "common.cuh"
 #include "mma_utils.cuh"
 
 #define AD_THREADS 128
-#define AD_CHUNK 128
+#define AD_SEG_PAGES 8
+#define AD_STAGES 3
 
 template <int D>
 __global__ void __launch_bounds__(AD_THREADS)
@@ -27,46 +31,45 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
                    int bt_stride, const int* __restrict__ seq_pos, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nq, int nkv, int window, float scale,
-                   int max_chunks, int* __restrict__ err, int* __restrict__ counters,
+                   int max_segs, int* __restrict__ err, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out) {
     pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;
-    extern __shared__ __align__(1024) unsigned char smem[];
-    unsigned char* Ks = smem;                    // 2 tiles
-    unsigned char* Vs = smem + 2 * TILE_BYTES;   // 2 tiles
-    __shared__ uint64_t bars[2];
+    extern __shared__ __align__(1024) unsigned char smem[];   // [stages][K tile, V tile]
+    __shared__ uint64_t full[AD_STAGES];
     __shared__ float s_m[4][16], s_l[4][16];
+    __shared__ int s_last;
 
-    const int c = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
+    const int seg = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int p = seq_pos[b];
     int lo = 0;
     if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
-    if (c < lo / AD_CHUNK || c > p / AD_CHUNK) return;
+    const int pg_lo = lo / LUMEN_PAGE, pg_hi = p / LUMEN_PAGE;
+    const int seg0 = pg_lo / AD_SEG_PAGES, seg1 = pg_hi / AD_SEG_PAGES;
+    if (seg < seg0 || seg > seg1) return;
+    const int pg_a = max(pg_lo, seg * AD_SEG_PAGES), pg_b = min(pg_hi, seg * AD_SEG_PAGES + AD_SEG_PAGES - 1);
+    const int npages = pg_b - pg_a + 1;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     const int G = nq / nkv;
+    const int* bt = block_table + (size_t)b * bt_stride;
 
     if (tid == 0) {
-        mbar_init(&bars[0], 1);
-        mbar_init(&bars[1], 1);
+        for (int i = 0; i < AD_STAGES; ++i) mbar_init(&full[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncthreads();
-    if (tid == 0) {
-        const int* bt = block_table + (size_t)b * bt_stride;
-        const int pg0 = bt[2 * c];
-        const int pg1 = (2 * c + 1 < bt_stride) ? bt[2 * c + 1] : 0;
-        const size_t t0 = ((size_t)pg0 * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
-        const size_t t1 = ((size_t)pg1 * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
-        mbar_expect_tx(&bars[0], 2 * TILE_BYTES);
-        bulk_load(Ks, kcache + t0, TILE_BYTES, &bars[0]);
-        bulk_load(Ks + TILE_BYTES, kcache + t1, TILE_BYTES, &bars[0]);
-        mbar_expect_tx(&bars[1], 2 * TILE_BYTES);
-        bulk_load(Vs, vcache + t0, TILE_BYTES, &bars[1]);
-        bulk_load(Vs + TILE_BYTES, vcache + t1, TILE_BYTES, &bars[1]);
-    }
+    auto issue = [&](int stage, int pg) {
+        const size_t off = ((size_t)bt[pg] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+        unsigned char* dst = smem + stage * 2 * TILE_BYTES;
+        mbar_expect_tx(&full[stage], 2 * TILE_BYTES);
+        bulk_load(dst, kcache + off, TILE_BYTES, &full[stage]);
+        bulk_load(dst + TILE_BYTES, vcache + off, TILE_BYTES, &full[stage]);
+    };
+    if (tid == 0)
+        for (int i = 0; i < AD_STAGES && i < npages; ++i) issue(i, pg_a + i);
 
     // Query fragments: rows = the G heads of this kv head (zero beyond G).
     uint32_t qa[D / 16][4];
@@ -84,97 +87,97 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
     }
 
-    const bool k_ok = mbar_wait(&bars[0], 0);
-    const uint32_t ktile = smem_u32(Ks) + (warp >> 1) * TILE_BYTES;
-    const uint32_t vtile = smem_u32(Vs) + (warp >> 1) * TILE_BYTES;
-    const int rb = (warp & 1) * 32;
-
-    // S = Q K^T for this warp's 32 keys.
-    float s[4][4];
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-        s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
-#pragma unroll
-        for (int kp = 0; kp < D / 32; ++kp) {
-            uint32_t r[4];
-            const int row = rb + 8 * nt + (lane & 7);
-            ldsm_x4(r, ktile + sw_off(row, 4 * kp + (lane >> 3)));
-            mma_bf16(s[nt], qa[2 * kp], r[0], r[1]);
-            mma_bf16(s[nt], qa[2 * kp + 1], r[2], r[3]);
-        }
-    }
-    // Mask, scale, softmax pieces of this warp (rows g and g + 8).
-    const int jbase = c * AD_CHUNK + warp * 32;
-    float m0 = -INFINITY, m1 = -INFINITY;
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            const int j = jbase + 8 * nt + 2 * t + i;
-            const bool valid = (j >= lo) && (j <= p);
-            s[nt][i] = valid ? s[nt][i] * scale : -INFINITY;
-            s[nt][2 + i] = valid ? s[nt][2 + i] * scale : -INFINITY;
-            m0 = fmaxf(m0, s[nt][i]);
-            m1 = fmaxf(m1, s[nt][2 + i]);
-        }
-    }
-    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 1));
-    m0 = fmaxf(m0, __shfl_xor_sync(0xffffffffu, m0, 2));
-    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 1));
-    m1 = fmaxf(m1, __shfl_xor_sync(0xffffffffu, m1, 2));
-    const float ms0 = (m0 == -INFINITY) ? 0.0f : m0, ms1 = (m1 == -INFINITY) ? 0.0f : m1;
-    float l0 = 0.0f, l1 = 0.0f;
-#pragma unroll
-    for (int nt = 0; nt < 4; ++nt) {
-#pragma unroll
-        for (int i = 0; i < 2; ++i) {
-            s[nt][i] = expf(s[nt][i] - ms0);
-            s[nt][2 + i] = expf(s[nt][2 + i] - ms1);
-            l0 += s[nt][i];
-            l1 += s[nt][2 + i];
-        }
-    }
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
-    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
-    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
-    uint32_t pa[2][4];
-#pragma unroll
-    for (int kk = 0; kk < 2; ++kk) {
-        pa[kk][0] = pack_bf16(s[2 * kk][0], s[2 * kk][1]);
-        pa[kk][1] = pack_bf16(s[2 * kk][2], s[2 * kk][3]);
-        pa[kk][2] = pack_bf16(s[2 * kk + 1][0], s[2 * kk + 1][1]);
-        pa[kk][3] = pack_bf16(s[2 * kk + 1][2], s[2 * kk + 1][3]);
-    }
-
-    // O = P V.
-    const bool v_ok = mbar_wait(&bars[1], 0);
     float o[D / 8][4];
 #pragma unroll
     for (int dt = 0; dt < D / 8; ++dt) o[dt][0] = o[dt][1] = o[dt][2] = o[dt][3] = 0.0f;
+    float m0 = -INFINITY, m1 = -INFINITY, l0 = 0.0f, l1 = 0.0f;   // rows g and g + 8 of this warp's keys
+    bool failed = false;
+    const int rb = warp * 16;                                     // this warp's keys within a page
+
+    for (int it = 0; it < npages; ++it) {
+        const int stage = it % AD_STAGES;
+        if (!mbar_wait(&full[stage], (it / AD_STAGES) & 1)) failed = true;
+        const uint32_t ktile = smem_u32(smem + stage * 2 * TILE_BYTES);
+        const uint32_t vtile = ktile + TILE_BYTES;
+
+        float s[2][4];
 #pragma unroll
-    for (int dtp = 0; dtp < D / 16; ++dtp) {
+        for (int nt = 0; nt < 2; ++nt) {
+            s[nt][0] = s[nt][1] = s[nt][2] = s[nt][3] = 0.0f;
 #pragma unroll
-        for (int kk = 0; kk < 2; ++kk) {
+            for (int kp = 0; kp < D / 32; ++kp) {
+                uint32_t r[4];
+                ldsm_x4(r, ktile + sw_off(rb + 8 * nt + (lane & 7), 4 * kp + (lane >> 3)));
+                mma_bf16(s[nt], qa[2 * kp], r[0], r[1]);
+                mma_bf16(s[nt], qa[2 * kp + 1], r[2], r[3]);
+            }
+        }
+        const int jbase = (pg_a + it) * LUMEN_PAGE + rb;
+        float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                const int j = jbase + 8 * nt + 2 * t + i;
+                const bool valid = (j >= lo) && (j <= p);
+                s[nt][i] = valid ? s[nt][i] * scale : -INFINITY;
+                s[nt][2 + i] = valid ? s[nt][2 + i] * scale : -INFINITY;
+                mx0 = fmaxf(mx0, s[nt][i]);
+                mx1 = fmaxf(mx1, s[nt][2 + i]);
+            }
+        }
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 1));
+        mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 2));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 1));
+        mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
+        const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
+        const float ms0 = (mn0 == -INFINITY) ? 0.0f : mn0, ms1 = (mn1 == -INFINITY) ? 0.0f : mn1;
+        const float c0 = (m0 == -INFINITY) ? 0.0f : expf(m0 - ms0);
+        const float c1 = (m1 == -INFINITY) ? 0.0f : expf(m1 - ms1);
+        float rs0 = 0.0f, rs1 = 0.0f;
+#pragma unroll
+        for (int nt = 0; nt < 2; ++nt) {
+#pragma unroll
+            for (int i = 0; i < 2; ++i) {
+                s[nt][i] = expf(s[nt][i] - ms0);
+                s[nt][2 + i] = expf(s[nt][2 + i] - ms1);
+                rs0 += s[nt][i];
+                rs1 += s[nt][2 + i];
+            }
+        }
+        rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1);
+        rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
+        rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1);
+        rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
+        l0 = l0 * c0 + rs0;
+        l1 = l1 * c1 + rs1;
+        m0 = mn0;
+        m1 = mn1;
+        uint32_t pa[4];
+        pa[0] = pack_bf16(s[0][0], s[0][1]);
+        pa[1] = pack_bf16(s[0][2], s[0][3]);
+        pa[2] = pack_bf16(s[1][0], s[1][1]);
+        pa[3] = pack_bf16(s[1][2], s[1][3]);
+#pragma unroll
+        for (int dtp = 0; dtp < D / 16; ++dtp) {
             uint32_t r[4];
             const int mi = lane >> 3;
-            const int row = rb + 16 * kk + (mi & 1) * 8 + (lane & 7);
-            ldsm_x4_t(r, vtile + sw_off(row, 2 * dtp + (mi >> 1)));
-            mma_bf16(o[2 * dtp], pa[kk], r[0], r[1]);
-            mma_bf16(o[2 * dtp + 1], pa[kk], r[2], r[3]);
+            ldsm_x4_t(r, vtile + sw_off(rb + (mi & 1) * 8 + (lane & 7), 2 * dtp + (mi >> 1)));
+            o[2 * dtp][0] *= c0; o[2 * dtp][1] *= c0; o[2 * dtp][2] *= c1; o[2 * dtp][3] *= c1;
+            o[2 * dtp + 1][0] *= c0; o[2 * dtp + 1][1] *= c0; o[2 * dtp + 1][2] *= c1; o[2 * dtp + 1][3] *= c1;
+            mma_bf16(o[2 * dtp], pa, r[0], r[1]);
+            mma_bf16(o[2 * dtp + 1], pa, r[2], r[3]);
         }
-    }
-    // One decision for the whole block (it is also the barrier before the K tiles are reused).
-    if (__syncthreads_or(!(k_ok && v_ok))) {
-        if (tid == 0) atomicExch(err, 1);
-        // a second bounded wait for the copies still in flight, then leave
-        mbar_wait(&bars[0], 0);
-        mbar_wait(&bars[1], 0);
-        return;
+        // every warp is done with this stage before it is refilled
+        if (__syncthreads_or(failed)) {
+            if (tid == 0) atomicExch(err, 1);
+            return;
+        }
+        if (tid == 0 && it + AD_STAGES < npages) issue(stage, pg_a + it + AD_STAGES);
     }
 
-    // Merge the four warps through shared memory (the K tiles are no longer read).
-    float* so = reinterpret_cast<float*>(Ks);   // [4][G][D]
+    // Merge the four warps through shared memory (all stages have been consumed).
+    float* so = reinterpret_cast<float*>(smem);   // [4][G][D]
     if (t == 0) {
         if (g < G) { s_m[warp][g] = m0; s_l[warp][g] = l0; }
         if (g + 8 < G) { s_m[warp][g + 8] = m1; s_l[warp][g + 8] = l1; }
@@ -193,9 +196,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
     }
     __syncthreads();
+    const bool single = (seg0 == seg1);     // the whole sequence was this block's
     for (int idx = tid; idx < G * D; idx += AD_THREADS) {
         const int row = idx / D, e = idx - row * D;
-        float M = fmaxf(fmaxf(s_m[0][row], s_m[1][row]), fmaxf(s_m[2][row], s_m[3][row]));
+        const float M = fmaxf(fmaxf(s_m[0][row], s_m[1][row]), fmaxf(s_m[2][row], s_m[3][row]));
         float acc = 0.0f, l = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
@@ -204,58 +208,59 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             acc += so[((size_t)(w * G + row)) * D + e] * f;
             l += s_l[w][row] * f;
         }
-        const size_t pi = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks + c;
-        part_o[pi * D + e] = acc;
-        if (e == 0) {
-            part_ml[pi * 2] = M;
-            part_ml[pi * 2 + 1] = l;
+        const size_t head = (size_t)b * nq + (size_t)kvh * G + row;
+        if (single) {
+            out[head * D + e] = __float2bfloat16_rn(acc * (1.0f / l));
+        } else {
+            const size_t pi = head * max_segs + seg;
+            part_o[pi * D + e] = acc;
+            if (e == 0) {
+                part_ml[pi * 2] = M;
+                part_ml[pi * 2 + 1] = l;
+            }
         }
     }
-    if (counters == nullptr) return;   // the chunks are merged by a second kernel
+    if (single || counters == nullptr) return;   // done, or a second kernel merges the segments
 
     // Merge without a second kernel and without waiting: every block of this (sequence, kv
     // head) counts itself in after its partials are visible; the one that counts last merges
-    // all chunks, in rising order whoever it is, and puts the counter back to zero.
-    __shared__ int s_last;
+    // all segments, in rising order whoever it is, and puts the counter back to zero.
     __threadfence();
     __syncthreads();
-    const int c0 = lo / AD_CHUNK, c1 = p / AD_CHUNK;
     if (tid == 0) {
         const int ticket = atomicAdd(&counters[b * nkv + kvh], 1);
-        s_last = (ticket == c1 - c0);
+        s_last = (ticket == seg1 - seg0);
         if (s_last) counters[b * nkv + kvh] = 0;
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    // weights of the chunks first (one thread per (row, chunk)), then the sums with all loads
-    // of a thread independent of one another
     constexpr int MAXC = 64;
-    float* s_f = reinterpret_cast<float*>(Vs);              // [G][MAXC] factors, then [G] 1/L
-    const int nch = c1 - c0 + 1;
+    float* s_f = so + 4 * 16 * D;              // [G][MAXC] factors, then [G] 1/L (past the warp sums)
+    const int nch = seg1 - seg0 + 1;
     if (nch <= MAXC) {
         for (int idx = tid; idx < G * nch; idx += AD_THREADS) {
             const int row = idx / nch, cc = idx - row * nch;
-            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks;
-            s_f[row * MAXC + cc] = __ldcg(part_ml + (base + c0 + cc) * 2);
+            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_segs;
+            s_f[row * MAXC + cc] = __ldcg(part_ml + (base + seg0 + cc) * 2);
         }
         __syncthreads();
         if (tid < G) {
             float M = -INFINITY;
             for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, s_f[tid * MAXC + cc]);
-            const size_t base = ((size_t)b * nq + (size_t)kvh * G + tid) * max_chunks;
+            const size_t base = ((size_t)b * nq + (size_t)kvh * G + tid) * max_segs;
             float L = 0.0f;
             for (int cc = 0; cc < nch; ++cc) {
                 const float f = expf(s_f[tid * MAXC + cc] - M);
                 s_f[tid * MAXC + cc] = f;
-                L += __ldcg(part_ml + (base + c0 + cc) * 2 + 1) * f;
+                L += __ldcg(part_ml + (base + seg0 + cc) * 2 + 1) * f;
             }
             s_f[G * MAXC + tid] = 1.0f / L;
         }
         __syncthreads();
         for (int idx = tid; idx < G * D; idx += AD_THREADS) {
             const int row = idx / D, e = idx - row * D;
-            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks + c0;
+            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_segs + seg0;
             float acc = 0.0f;
 #pragma unroll 4
             for (int cc = 0; cc < nch; ++cc) acc += __ldcg(part_o + (base + cc) * D + e) * s_f[row * MAXC + cc];
@@ -266,11 +271,11 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
     for (int idx = tid; idx < G * D; idx += AD_THREADS) {
         const int row = idx / D, e = idx - row * D;
-        const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_chunks;
+        const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_segs;
         float M = -INFINITY;
-        for (int cc = c0; cc <= c1; ++cc) M = fmaxf(M, __ldcg(part_ml + (base + cc) * 2));
+        for (int cc = seg0; cc <= seg1; ++cc) M = fmaxf(M, __ldcg(part_ml + (base + cc) * 2));
         float L = 0.0f, acc = 0.0f;
-        for (int cc = c0; cc <= c1; ++cc) {
+        for (int cc = seg0; cc <= seg1; ++cc) {
             const float f = expf(__ldcg(part_ml + (base + cc) * 2) - M);
             L += __ldcg(part_ml + (base + cc) * 2 + 1) * f;
             acc += __ldcg(part_o + (base + cc) * D + e) * f;
@@ -279,20 +284,21 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     }
 }
 
-// Merges the chunks of one (sequence, head) in rising order.
+// Merges the segments of one (sequence, head) in rising order (used when no counters are given).
 template <typename TOut>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
                                            const float* __restrict__ part_ml,
                                            const int* __restrict__ seq_pos, TOut* __restrict__ out,
-                                           int nq, int D, int window, int max_chunks) {
+                                           int nq, int D, int window, int max_segs) {
     pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     const int head = blockIdx.x, b = blockIdx.y;
     const int p = seq_pos[b];
     int lo = 0;
     if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
-    const int c0 = lo / AD_CHUNK, c1 = p / AD_CHUNK;
-    const size_t base = ((size_t)b * nq + head) * max_chunks;
+    const int c0 = lo / LUMEN_PAGE / AD_SEG_PAGES, c1 = p / LUMEN_PAGE / AD_SEG_PAGES;
+    if (c0 == c1) return;       // a single segment: the first kernel has written the result
+    const size_t base = ((size_t)b * nq + head) * max_segs;
     float M = -INFINITY;
     for (int c = c0; c <= c1; ++c) M = fmaxf(M, part_ml[(base + c) * 2]);
     float L = 0.0f;
@@ -307,45 +313,51 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
 }
 
 // Entry point. q, out: bfloat16 [B, nq, D]; caches in the swizzled layout; seq_pos[b] is the
-// position of sequence b's query (its cached length before this token). part_o and part_ml are
-// the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
-// counters: null (a second kernel merges the chunks), or B * nkv ints that are zero before the
-// call and zero again after it (the last block of each group merges).
+// position of sequence b's query (its cached length before this token). max_segs: segments
+// (of 8 pages) that the page table can hold, at least ceil(bt_stride / 8). part_o and part_ml
+// are the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
+// counters: null (a second kernel merges the segments), or B * nkv ints that are zero before
+// the call and zero again after it (the last block of each group merges).
 LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* vcache,
                                 const int* block_table, int bt_stride, const int* seq_pos,
                                 void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
-                                int d, int window, float scale, int max_chunks, int* err,
+                                int d, int window, float scale, int max_segs, int* err,
                                 int* counters, cudaStream_t stream) {
     if (B <= 0) return 0;
-    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || max_chunks <= 0)
+    if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || max_segs <= 0)
         return LUMEN_ERR_UNSUPPORTED;
     if (B > 65535 || nkv > 65535) return LUMEN_ERR_UNSUPPORTED;
-    if (2 * max_chunks > bt_stride + 1) return LUMEN_ERR_BAD_ARGUMENT;
-    dim3 grid(max_chunks, nkv, B);
+    if (AD_SEG_PAGES * max_segs < bt_stride) return LUMEN_ERR_BAD_ARGUMENT;
+    dim3 grid(max_segs, nkv, B);
     const __nv_bfloat16* qp = (const __nv_bfloat16*)q;
     const __nv_bfloat16* kp = (const __nv_bfloat16*)kcache;
     const __nv_bfloat16* vp = (const __nv_bfloat16*)vcache;
+    cudaError_t e;
     if (d == 128) {
-        const int smem = 4 * LUMEN_PAGE * 128 * 2;
+        const int smem = AD_STAGES * 2 * LUMEN_PAGE * 128 * 2;
         auto k = attn_decode_kernel<128>;
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        lumen_launch(k, dim3(grid), dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
-                                              nq, nkv, window, scale, max_chunks, err, counters,
-                                              (__nv_bfloat16*)out);
+        e = lumen_launch(k, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos,
+                         part_o, part_ml, nq, nkv, window, scale, max_segs, err, counters,
+                         (__nv_bfloat16*)out);
     } else if (d == 64) {
-        const int smem = 4 * LUMEN_PAGE * 64 * 2;
+        const int smem = AD_STAGES * 2 * LUMEN_PAGE * 64 * 2;
         auto k = attn_decode_kernel<64>;
-        lumen_launch(k, dim3(grid), dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos, part_o, part_ml,
-                                              nq, nkv, window, scale, max_chunks, err, counters,
-                                              (__nv_bfloat16*)out);
+        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        e = lumen_launch(k, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos,
+                         part_o, part_ml, nq, nkv, window, scale, max_segs, err, counters,
+                         (__nv_bfloat16*)out);
     } else {
         return LUMEN_ERR_UNSUPPORTED;
     }
+    if (e != cudaSuccess) return (int)e;
     LUMEN_LAUNCH_CHECK();
     if (counters != nullptr) return 0;
     dim3 cgrid(nq, B);
-    lumen_launch(attn_decode_combine_kernel<__nv_bfloat16>, dim3(cgrid), dim3(128), 0, stream, 
-        part_o, part_ml, seq_pos, (__nv_bfloat16*)out, nq, d, window, max_chunks);
+    e = lumen_launch(attn_decode_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream,
+                     (const float*)part_o, (const float*)part_ml, seq_pos, (__nv_bfloat16*)out, nq, d, window,
+                     max_segs);
+    if (e != cudaSuccess) return (int)e;
     LUMEN_LAUNCH_CHECK();
     return 0;
 }
@@ -372,18 +384,18 @@ static std::mutex s_scratch_lock;
 LUMEN_API int lumen_attn_decode_noalloc(const void* q, const void* kcache, const void* vcache,
                                         const int* block_table, int bt_stride, const int* seq_pos,
                                         void* out, int B, int nq, int nkv, int d, int window,
-                                        float scale, int max_chunks, int* err, cudaStream_t stream) {
+                                        float scale, int max_segs, int* err, cudaStream_t stream) {
     if (B <= 0) return 0;
-    if (nq <= 0 || max_chunks <= 0 || d <= 0) return LUMEN_ERR_UNSUPPORTED;
+    if (nq <= 0 || max_segs <= 0 || d <= 0) return LUMEN_ERR_UNSUPPORTED;
     const unsigned long long rows = (unsigned long long)B * (unsigned long long)nq *
-                                    (unsigned long long)max_chunks;
+                                    (unsigned long long)max_segs;
     const unsigned long long need = rows * (unsigned long long)(d + 2);
     if (need > (unsigned long long)LUMEN_DECODE_NOALLOC_MAX_FLOATS) {
         std::fprintf(stderr,
-                     "lumen_attn_decode_noalloc: batch %d x heads %d x chunks %d x (head size %d + 2) = "
+                     "lumen_attn_decode_noalloc: batch %d x heads %d x segments %d x (head size %d + 2) = "
                      "%llu floats of scratch, the built-in array holds %llu; use a smaller batch or "
                      "page table, or the allocating entry point lumen_attn_decode\n",
-                     B, nq, max_chunks, d, need, (unsigned long long)LUMEN_DECODE_NOALLOC_MAX_FLOATS);
+                     B, nq, max_segs, d, need, (unsigned long long)LUMEN_DECODE_NOALLOC_MAX_FLOATS);
         return LUMEN_ERR_SCRATCH_TOO_SMALL;
     }
     int dev = -1;
@@ -402,11 +414,11 @@ LUMEN_API int lumen_attn_decode_noalloc(const void* q, const void* kcache, const
         }
         scratch = s_scratch_on_device[dev];
     }
-    // Nothing in the scratch has to start at zero: every (sequence, head, chunk) entry that
+    // Nothing in the scratch has to start at zero: every (sequence, head, segment) entry that
     // the merge kernel reads is written in full by this call's first kernel; entries of
-    // chunks outside a sequence's range keep older contents and are never read.
+    // segments outside a sequence's range keep older contents and are never read.
     float* part_o = scratch;
     float* part_ml = scratch + rows * (unsigned long long)d;
     return lumen_attn_decode(q, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml,
-                             B, nq, nkv, d, window, scale, max_chunks, err, nullptr, stream);
+                             B, nq, nkv, d, window, scale, max_segs, err, nullptr, stream);
 }

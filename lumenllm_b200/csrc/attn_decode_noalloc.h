@@ -10,8 +10,8 @@
 // that must not grow it; real-time style serving loops that forbid cudaMalloc/cudaFree on the
 // hot path because both can stall the whole device; and plain C or Rust callers that link this
 // shared object without PyTorch and have no caching allocator to lean on. The ordinary entry
-// point, lumen_attn_decode, asks its caller for two scratch buffers (the per-chunk partial
-// results); this one keeps them in a fixed array that belongs to the library itself.
+// point, lumen_attn_decode, asks its caller for two scratch buffers (the partial results of the
+// segments a long sequence is cut into); this one keeps them in a fixed array that belongs to the library itself.
 //
 // What it does. Exactly what lumen_attn_decode does, with the same kernels: inputs and the
 // output are the caller's (q, the paged K and V caches in the swizzled layout, the page table,
@@ -21,10 +21,11 @@
 // loaded holds these 16 MiB from the first use of the library on that GPU until the process
 // exits.
 //
-// Limits. The call needs B * nq * max_chunks * (d + 2) floats. If that is more than the array
-// holds, nothing is launched, a line that names the four numbers goes to stderr, and
-// LUMEN_ERR_SCRATCH_TOO_SMALL is returned. (For 32 query heads of size 128: up to 31 sequences
-// with page tables of 64 pages, i.e. 4,096 positions; 64 sequences with 30 pages.)
+// Limits. max_segs is the number of 8-page segments the page table can hold, at least
+// ceil(bt_stride / 8). The call needs B * nq * max_segs * (d + 2) floats. If that is more than
+// the array holds, nothing is launched, a line that names the four numbers goes to stderr, and
+// LUMEN_ERR_SCRATCH_TOO_SMALL is returned. (For 32 query heads of size 128: up to 126 sequences
+// with page tables of 64 pages, i.e. 4,096 positions; 31 sequences with 256 pages.)
 // Other return values are those of lumen_attn_decode (0 = launched, a cudaError_t, or
 // LUMEN_ERR_UNSUPPORTED / LUMEN_ERR_BAD_ARGUMENT).
 //
@@ -48,4 +49,4 @@
 extern "C" int lumen_attn_decode_noalloc(const void* q, const void* kcache, const void* vcache,
                                          const int* block_table, int bt_stride, const int* seq_pos,
                                          void* out, int B, int nq, int nkv, int d, int window,
-                                         float scale, int max_chunks, int* err, cudaStream_t stream);
+                                         float scale, int max_segs, int* err, cudaStream_t stream);

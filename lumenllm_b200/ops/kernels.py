@@ -324,15 +324,15 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     if seq_pos.numel() < B or block_table.shape[0] < B:
         raise KernelError("attn_decode: metadata shorter than the batch")
     width = block_table.shape[1]
-    max_chunks = (width + 1) // 2
+    max_segs = (width + 7) // 8          # a block walks a segment of 8 pages
     out = torch.empty_like(q)
-    part_o = torch.empty((B, nq, max_chunks, d), dtype=F32, device=q.device)
-    part_ml = torch.empty((B, nq, max_chunks, 2), dtype=F32, device=q.device)
+    part_o = torch.empty((B, nq, max_segs, d), dtype=F32, device=q.device)
+    part_ml = torch.empty((B, nq, max_segs, 2), dtype=F32, device=q.device)
     counters = _decode_counters(q.device) if B * nkv <= _COUNTERS else None
     f = fn("attn_decode", "lumen_attn_decode",
            [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(seq_pos),
-            ptr(out), ptr(part_o), ptr(part_ml), B, nq, nkv, d, int(window), float(scale), max_chunks,
+            ptr(out), ptr(part_o), ptr(part_ml), B, nq, nkv, d, int(window), float(scale), max_segs,
             ptr(error_flag(q.device)), ptr(counters), stream_ptr()), "attn_decode")
     return out
 

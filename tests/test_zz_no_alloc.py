@@ -4,7 +4,7 @@ PyTorch's allocator would call it: through its exported C symbol, with raw devic
 Such callers exist: code running inside another framework's allocator hooks, plug-ins with a
 memory budget fixed at start-up, serving loops that forbid cudaMalloc on the hot path, C or Rust
 programs that link the shared object directly. For them `lumen_attn_decode_noalloc` keeps the
-per-chunk partial results in an array that is part of the library. This test checks, on two
+partial results of a long sequence's segments in an array that is part of the library. This test checks, on two
 calls in a row with different batches (the second meets what the first left in the array), that
 it returns what the ordinary entry point returns, and that a batch too large for the array is
 refused without a launch.
@@ -53,7 +53,7 @@ def _call(f, q, kc, vc, table, pos, window, err):
     out = torch.empty_like(q)
     rc = f(q.data_ptr(), kc.data_ptr(), vc.data_ptr(), table.data_ptr(), table.stride(0),
            pos.data_ptr(), out.data_ptr(), B, nq, kc.shape[1], d, window, float(d) ** -0.5,
-           (table.shape[1] + 1) // 2, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
+           (table.shape[1] + 7) // 8, err.data_ptr(), torch.cuda.current_stream().cuda_stream)
     return rc, out
 
 
@@ -88,8 +88,8 @@ def test_no_alloc_entry_point_matches_the_allocating_one_twice():
 def test_no_alloc_entry_point_refuses_what_does_not_fit(capfd):
     f = _noalloc_fn()
     err = torch.zeros(1, dtype=torch.int32, device="cuda")
-    B, nq, nkv, d, width = 64, 32, 8, 128, 64
-    assert B * nq * ((width + 1) // 2) * (d + 2) > MAX_FLOATS
+    B, nq, nkv, d, width = 64, 32, 8, 128, 256
+    assert B * nq * ((width + 7) // 8) * (d + 2) > MAX_FLOATS
     q, kc, vc, table, pos = _case(B, nq, nkv, d, [10] * B, 80, width, 30)
     rc, out = _call(f, q, kc, vc, table, pos, 0, err)
     assert rc == ERR_SCRATCH_TOO_SMALL
