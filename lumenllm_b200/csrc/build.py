@@ -34,6 +34,7 @@ MODULES = {
     "sample": (["sample.cu"], ["common.cuh"]),
     "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "attn_decode_noalloc.h"]),
     "attn_prefill": (["attn_prefill.cu"], ["common.cuh", "mma_utils.cuh"]),
+    "attn_prefill_tc": (["attn_prefill_tc.cu"], ["common.cuh", "mma_utils.cuh"]),
 }
 
 NVCC_FLAGS = [

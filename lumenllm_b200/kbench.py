@@ -53,6 +53,7 @@ def main(argv=None):
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
     ap.add_argument("--silu", action="store_true")
+    ap.add_argument("--mma-sync", action="store_true", help="attn_prefill: the mma.sync kernel")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--len", type=int, default=1600)
     ap.add_argument("--tokens", type=int, default=2048)
@@ -90,7 +91,8 @@ def main(argv=None):
         q = torch.randn(a.tokens, a.heads, a.head_dim, device=dev).to(bf)
         cu = torch.tensor([0, a.tokens], dtype=torch.int32, device=dev)
         st = torch.zeros(1, dtype=torch.int32, device=dev)
-        fns = [lambda: K.attn_prefill(q, kc, vc, table, cu, st, [a.tokens], 0, a.head_dim ** -0.5)]
+        fns = [lambda: K.attn_prefill(q, kc, vc, table, cu, st, [a.tokens], 0, a.head_dim ** -0.5,
+                                      tensor_memory=not a.mma_sync)]
         us = _time(fns, a.reps)
         flops = 2.0 * a.tokens * a.tokens * a.head_dim * a.heads      # causal: half of 4 T^2 d
         note = f"{flops / us / 1e6:.1f} TFLOP/s"

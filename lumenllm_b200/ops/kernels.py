@@ -337,10 +337,12 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     return out
 
 
-def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window, scale):
+def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window, scale,
+                 tensor_memory=True):
     """Causal flash attention for sequences that bring q_lens[b] tokens each (host list),
     bfloat16, swizzled cache, head size 64 or 128, at most 16 query heads per kv head.
-    q [N, nq, d]; cu_q int32 [B+1]; seq_start int32 [B]."""
+    q [N, nq, d]; cu_q int32 [B+1]; seq_start int32 [B]. With tensor_memory the tcgen05
+    kernel (128 rows a block, S and O in tensor memory), else the mma.sync kernel (64 rows)."""
     N, nq, d = q.shape
     nkv = kcache.shape[1]
     B = len(q_lens)
@@ -354,10 +356,11 @@ def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window
         raise KernelError("attn_prefill: at most 16 query heads per kv head")
     if cu_q.numel() < B + 1 or seq_start.numel() < B or block_table.shape[0] < B or sum(q_lens) != N:
         raise KernelError("attn_prefill: metadata does not match the batch")
-    tq = 64 // (nq // nkv)
+    tq = (128 if tensor_memory else 64) // (nq // nkv)
     n_tiles = sum((n + tq - 1) // tq for n in q_lens)
     out = torch.empty_like(q)
-    f = fn("attn_prefill", "lumen_attn_prefill",
+    f = fn("attn_prefill_tc" if tensor_memory else "attn_prefill",
+           "lumen_attn_prefill_tc" if tensor_memory else "lumen_attn_prefill",
            [P, P, P, P, c_int, P, P, c_int, c_int, P, c_int, c_int, c_int, c_int, c_float, P, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(cu_q),
             ptr(seq_start), B, n_tiles, ptr(out), nq, nkv, d, int(window), float(scale),

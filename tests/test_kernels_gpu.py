@@ -269,9 +269,10 @@ def test_attention_decode_kernel(nq, nkv, d, window):
     assert torch.equal(out, out2)
 
 
+@pytest.mark.parametrize("tensor_memory", [True, False])
 @pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, 0), (4, 2, 64, 0), (6, 2, 64, 0), (5, 1, 128, 0),
                                             (16, 1, 64, 0), (2, 2, 128, 0), (8, 2, 128, 70), (4, 2, 64, 24)])
-def test_attention_prefill_kernel(nq, nkv, d, window):
+def test_attention_prefill_kernel(nq, nkv, d, window, tensor_memory):
     """Flash attention for prompts: whole prompts, continuations from a cached prefix, and
     single tokens, of unequal lengths in one batch."""
     from lumenllm_b200.ops import kernels as K
@@ -280,14 +281,14 @@ def test_attention_prefill_kernel(nq, nkv, d, window):
     cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=I32)
     out = K.attn_prefill(dev(torch.cat(qs).to(BF16)), dev(to_sw128(kc.to(BF16))), dev(to_sw128(vc.to(BF16))),
                          dev(table), dev(cu), dev(torch.tensor(starts, dtype=I32)), lens, window,
-                         d ** -0.5).cpu().float()
+                         d ** -0.5, tensor_memory=tensor_memory).cpu().float()
     K.check_error_flags()
     ref = _attn_ref(qs, ks, vs, lens, starts, window, BF16)
     err = (out - ref).abs().max(dim=-1).values.max(dim=-1).values
     assert float(err.max()) < 2 ** -6, (int(err.argmax()), float(err.max()))
 
 
-@pytest.mark.parametrize("kernel", ["decode", "prefill"])
+@pytest.mark.parametrize("kernel", ["decode", "prefill", "prefill_mma"])
 def test_fast_attention_one_far_key_and_the_windows_edge(kernel):
     from lumenllm_b200.ops import kernels as K
     nq, nkv, d, T = 4, 1, 128, 700
@@ -310,7 +311,8 @@ def test_fast_attention_one_far_key_and_the_windows_edge(kernel):
             out = K.attn_decode(*args, dev(torch.tensor([T - 1], dtype=I32)), window, d ** -0.5)
         else:
             out = K.attn_prefill(*args, dev(torch.tensor([0, 1], dtype=I32)),
-                                 dev(torch.tensor([T - 1], dtype=I32)), [1], window, d ** -0.5)
+                                 dev(torch.tensor([T - 1], dtype=I32)), [1], window, d ** -0.5,
+                                 tensor_memory=(kernel == "prefill"))
         out = out.cpu().float()
         K.check_error_flags()
         target = v[far, 0].to(BF16).float()
