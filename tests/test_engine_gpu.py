@@ -323,3 +323,35 @@ def test_trace_run_program(tmp_path, plain, tiny_models):
         assert not (out / "2.f32").exists()
         check(rd(3), ra[32:33], dtype, "trace step 3")
         check(rd(4), rc[69:70], dtype, "trace step 4")
+
+
+@pytest.mark.parametrize("shape", ["14b", "32b"])
+def test_serving_kernels_at_real_layer_sizes_agree_with_the_32_bit_path(shape):
+    """One layer of the 14B / 32B shapes (width 5120, 40 or 64 heads in groups of 5 or 8, q width
+    unequal to the width, the full vocabulary) with random bfloat16 weights: the bfloat16 path
+    (tcgen05 products and attention, streaming products, split-KV decode) against the true
+    32-bit path of the same weights, for a prompt, a continuation and decoded tokens."""
+    from lumenllm_b200 import Engine, StepEntry
+    dims = {"14b": dict(hidden_size=5120, num_attention_heads=40, intermediate_size=17408),
+            "32b": dict(hidden_size=5120, num_attention_heads=64, intermediate_size=25600)}[shape]
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=1,
+               num_key_value_heads=8, head_dim=128, vocab_size=151936, rope_theta=1000000.0,
+               rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False, **dims)
+    toks = seeded_tokens(151936, [300, 70, 1], 5)
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(cfg, seed=3, std=0.02, norm_jitter=0.1, dtype=dtype, max_tokens=2048)
+        slots = [eng.alloc_slot() for _ in toks]
+        a = eng.step([StepEntry(s, t[:max(1, len(t) - 40)], [max(1, len(t) - 40) - 1])
+                      for s, t in zip(slots, toks)])
+        b = eng.step([StepEntry(slots[0], toks[0][260:290], [0, 29]), StepEntry(slots[1], toks[1][30:31], [0])])
+        c = [eng.step([StepEntry(slots[0], [toks[0][290 + k]], [0]), StepEntry(slots[1], [toks[1][31 + k]], [0])])
+             for k in range(3)]
+        outs[dtype] = torch.cat([a, b] + c).float().cpu()
+        del eng
+        torch.cuda.empty_cache()
+    from lumenllm_b200.ops import kernels as K
+    K.check_error_flags()
+    ref, got = outs["float32"], outs["bfloat16"]
+    assert torch.isfinite(got).all()
+    assert float((got - ref).abs().max()) <= tolerance("bfloat16", ref)
