@@ -98,7 +98,7 @@ def _compile(module: str, out_dir: Path) -> Path:
     srcs, _ = MODULES[module]
     final = out_dir / f"lumen_{module}.{_digest(module)}.so"
     tmp = out_dir / f".lumen_{module}.{os.getpid()}.{threading.get_ident()}.tmp.so"
-    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(tmp)] + [str(CSRC / s) for s in srcs]
+    cmd = [_nvcc(), *NVCC_FLAGS, f'-DLUMEN_MODULE="{module}"', "-I", str(CSRC), "-o", str(tmp)] + [str(CSRC / s) for s in srcs]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)

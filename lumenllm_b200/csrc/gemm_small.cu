@@ -22,6 +22,15 @@
 #define GS_THREADS (GS_WARPS * 32)
 #define GS_ROWS (GS_WARPS * 16)   // rows of W per block
 #define GS_UNROLL 4               // 64-wide k chunks in flight per warp
+#define GS_SLOTS 296              // blocks that run at a time: two on each of 148 SMs
+#define GS_UNIT 32                // k slices are cut in units of 32 values (64 bytes)
+
+// First k of slice s of S: the units of K dealt out evenly, so slices differ by one unit at most.
+__host__ __device__ __forceinline__ int gs_slice_begin(int s, int S, int K) {
+    const int units = (K + GS_UNIT - 1) / GS_UNIT;
+    const int k = (int)(((long long)s * units) / S) * GS_UNIT;
+    return k < K ? k : K;
+}
 
 __device__ __forceinline__ uint4 ldg_stream(const void* p) {
     uint4 v;
@@ -95,11 +104,11 @@ __device__ __forceinline__ void stage_x(const void* x, int XS, __nv_bfloat16* xs
 template <int NT, int MODE>   // NT: n-tiles of 8 batch rows (M <= 8 NT)
 __global__ void __launch_bounds__(GS_THREADS)
 gemm_small_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ W,
-                  float* __restrict__ out, int M, int N, int K, int kslice, int XS) {
+                  float* __restrict__ out, int M, int N, int K, int S, int XS) {
     extern __shared__ __align__(16) unsigned char smem_raw[];
     __nv_bfloat16* xs = reinterpret_cast<__nv_bfloat16*>(smem_raw);
-    const int k0 = blockIdx.y * kslice;
-    const int klen = min(kslice, K - k0);          // a multiple of 64 except possibly at the end of K
+    const int k0 = gs_slice_begin(blockIdx.y, S, K);
+    const int klen = gs_slice_begin(blockIdx.y + 1, S, K) - k0;   // a multiple of 32 except at the end of K
     const int kpad = (klen + 63) & ~63;
     const int xstride = kpad + 32;                 // +64 bytes: rows 16 banks apart, no conflicts
     constexpr int MP = 8 * NT;
@@ -183,19 +192,28 @@ gemm_small_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ 
     }
 }
 
-// Number of k splits for a weight of shape [N, K]: enough blocks for two waves on 148 SMs,
-// slices that are multiples of 64 and not shorter than 512. A function of (N, K) only.
+// Number of k splits for a weight of shape [N, K]. Two blocks of this kernel fit on an SM, so
+// 296 run at a time; S is chosen so that the row blocks times S fill whole waves of 296 as
+// nearly as possible (the smaller S on a tie), with slices no shorter than 256. A function of
+// (N, K) only. Slices are cut in units of 32 values (64 bytes) and differ by one unit at most.
 LUMEN_API int lumen_gemm_small_splits(int N, int K) {
     const int row_blocks = (N + GS_ROWS - 1) / GS_ROWS;
-    int s = (2 * 148 + row_blocks - 1) / row_blocks;
-    const int max_s = K / 512 > 0 ? K / 512 : 1;
-    if (s > max_s) s = max_s;
-    if (s < 1) s = 1;
-    // slices of equal length, multiple of 64
-    int slice = ((K + s - 1) / s + 63) & ~63;
-    return (K + slice - 1) / slice;
+    const int units = (K + GS_UNIT - 1) / GS_UNIT;
+    int max_s = K / 256;
+    if (max_s > 16) max_s = 16;
+    if (max_s < 1) max_s = 1;
+    int best = 1;
+    double best_fill = 0.0;
+    for (int s = 1; s <= max_s; ++s) {
+        const int blocks = row_blocks * s;
+        const int waves = (blocks + GS_SLOTS - 1) / GS_SLOTS;
+        // the longest slice against the mean one: uneven cuts cost as empty slots do
+        const int longest = (units + s - 1) / s;
+        const double fill = (double)blocks / (waves * GS_SLOTS) * ((double)units / s) / longest;
+        if (fill > best_fill + 0.02) { best_fill = fill; best = s; }
+    }
+    return best;
 }
-
 // x: mode 0 bfloat16 [M, K]; mode 1 float32 [x_splits, M, 2K] (partials of gate | up;
 // SiLU(gate)*up is applied to their sum); mode 2 the same with gate_i, up_i in columns
 // 2i, 2i + 1. out: float32 [S, M, N] with
@@ -205,7 +223,7 @@ LUMEN_API int lumen_gemm_small(const void* x, int mode, int x_splits, const void
     if (M <= 0 || N <= 0) return 0;
     if (M > 16 || K <= 0 || (K & 7) || mode < 0 || mode > 2 || x_splits < 1) return LUMEN_ERR_UNSUPPORTED;
     const int S = lumen_gemm_small_splits(N, K);
-    const int slice = ((K + S - 1) / S + 63) & ~63;
+    const int slice = (((K + GS_UNIT - 1) / GS_UNIT + S - 1) / S * GS_UNIT + 63) & ~63;   // the longest, padded
     const int NT = (M + 7) / 8;
     const size_t smem = (size_t)(8 * NT) * (slice + 32) * 2;
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
@@ -216,7 +234,7 @@ LUMEN_API int lumen_gemm_small(const void* x, int mode, int x_splits, const void
         auto k = gemm_small_kernel<NT_, MODE_>;                                                    \
         if (smem > 48 * 1024)                                                                      \
             cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);       \
-        lumen_launch(k, dim3(grid), dim3(GS_THREADS), smem, stream, x, Wp, out, M, N, K, slice, x_splits);               \
+        lumen_launch(k, dim3(grid), dim3(GS_THREADS), smem, stream, x, Wp, out, M, N, K, S, x_splits);               \
     } while (0)
     if (NT == 1 && mode == 0) GS_LAUNCH(1, 0);
     else if (NT == 1 && mode == 1) GS_LAUNCH(1, 1);

@@ -23,14 +23,22 @@ from .ops import kernels as K
 
 
 def _time(fns, reps):
+    """Microseconds per launch. The calls of one pass are captured in a CUDA graph and the
+    graph is replayed, so that what is timed is the device's work and not the host's launch
+    path (a Python launch costs more than a short kernel runs)."""
     for f in fns:
         f()
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    with torch.cuda.graph(graph):
+        for f in fns:
+            f()
+    graph.replay()
     torch.cuda.synchronize()
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     e0.record()
     for _ in range(reps):
-        for f in fns:
-            f()
+        graph.replay()
     e1.record()
     torch.cuda.synchronize()
     return e0.elapsed_time(e1) * 1000.0 / (reps * len(fns))
