@@ -1,7 +1,7 @@
 // Decode attention over the paged cache for bfloat16, split over the keys.
 //
-// One query token per sequence. A block takes one SEGMENT of a sequence (8 pages = 512 keys)
-// for one kv head and serves all query heads of that kv head at once, so every key and value
+// One query token per sequence. A block takes one SEGMENT of a sequence (a run of at most
+// seg_pages pages; a sequence's pages are dealt out evenly over its segments) for one kv head and serves all query heads of that kv head at once, so every key and value
 // is read from HBM exactly once per step. The block walks its pages through a three-stage
 // ring: the K tile and the V tile of a page are each one contiguous, already swizzled block
 // of the cache and are brought in by one bulk asynchronous copy each (cp.async.bulk,
@@ -13,17 +13,45 @@
 // that fits one segment is finished there; otherwise the block writes one partial
 // (unnormalised O, running max m, sum l) per (sequence, head, segment) and the segments are
 // merged in rising order, either by the block of the group that finishes last (it learns
-// that from a counter; nobody waits) or by a second kernel. Segment and page edges are
-// multiples of 512 and 64 in absolute position, so the result for a token does not depend
-// on its neighbours in the batch.
+// that from a counter; nobody waits) or by a second kernel. How a sequence is cut depends on
+// its own length, the window and seg_pages only, and a key's place inside its page never
+// changes, so neighbours in the batch do not change a token's result.
+//
+// The positions, the page table and every page but the one that holds the newest token were
+// written before the kernel ahead of this one started, so the block requests its first pages
+// before it waits for that kernel (programmatic dependent launch); the newest page and the
+// query come after the wait.
 //
 // Scratch: part_o [B, nq, max_segs, D] and part_ml [B, nq, max_segs, 2] float32.
 #include "common.cuh"
 #include "mma_utils.cuh"
 
 #define AD_THREADS 128
-#define AD_SEG_PAGES 8
+#define AD_SEG_PAGES 8            // the largest seg_pages a caller may ask for
+#define AD_MAX_SEGS 32            // a sequence is never cut into more segments than this
 #define AD_STAGES 3
+
+// The pages [pg_lo, pg_hi] that the query at position p sees, cut into nseg segments of
+// per or per + 1 pages (the first rem have one more): segments of seg_pages pages at most,
+// unless that would make more than AD_MAX_SEGS of them. Nothing here depends on the width of
+// the page table.
+struct SegPlan {
+    int lo, pg_lo, pg_hi, nseg, per, rem;
+    __device__ __forceinline__ int first(int seg) const { return pg_lo + seg * per + min(seg, rem); }
+    __device__ __forceinline__ int count(int seg) const { return per + (seg < rem ? 1 : 0); }
+};
+__device__ __forceinline__ SegPlan seg_plan(int p, int window, int seg_pages) {
+    SegPlan s;
+    s.lo = 0;
+    if (window > 0 && p - window + 1 > 0) s.lo = p - window + 1;
+    s.pg_lo = s.lo / LUMEN_PAGE;
+    s.pg_hi = p / LUMEN_PAGE;
+    const int np = s.pg_hi - s.pg_lo + 1;
+    s.nseg = min((np + seg_pages - 1) / seg_pages, AD_MAX_SEGS);
+    s.per = np / s.nseg;
+    s.rem = np - s.per * s.nseg;
+    return s;
+}
 
 template <int D>
 __global__ void __launch_bounds__(AD_THREADS)
@@ -31,10 +59,8 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
                    int bt_stride, const int* __restrict__ seq_pos, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nq, int nkv, int window, float scale,
-                   int max_segs, int* __restrict__ err, int* __restrict__ counters,
+                   int max_segs, int seg_pages, int* __restrict__ err, int* __restrict__ counters,
                    __nv_bfloat16* __restrict__ out) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
-    pdl_trigger();
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;
     extern __shared__ __align__(1024) unsigned char smem[];   // [stages][K tile, V tile]
     __shared__ uint64_t full[AD_STAGES];
@@ -42,14 +68,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     __shared__ int s_last;
 
     const int seg = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
-    const int p = seq_pos[b];
-    int lo = 0;
-    if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
-    const int pg_lo = lo / LUMEN_PAGE, pg_hi = p / LUMEN_PAGE;
-    const int seg0 = pg_lo / AD_SEG_PAGES, seg1 = pg_hi / AD_SEG_PAGES;
-    if (seg < seg0 || seg > seg1) return;
-    const int pg_a = max(pg_lo, seg * AD_SEG_PAGES), pg_b = min(pg_hi, seg * AD_SEG_PAGES + AD_SEG_PAGES - 1);
-    const int npages = pg_b - pg_a + 1;
+    const int p = seq_pos[b];                   // written before the step's first kernel
+    const SegPlan plan = seg_plan(p, window, seg_pages);
+    if (seg >= plan.nseg) return;
+    const int lo = plan.lo, pg_a = plan.first(seg), npages = plan.count(seg), pg_hi = plan.pg_hi;
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
@@ -68,8 +90,21 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         bulk_load(dst, kcache + off, TILE_BYTES, &full[stage]);
         bulk_load(dst + TILE_BYTES, vcache + off, TILE_BYTES, &full[stage]);
     };
+    // The first pages of the ring, as far as they are older than this step; then wait for the
+    // kernel ahead (it writes the newest token's key and value, and the query), then the rest.
+    int issued = 0;
     if (tid == 0)
-        for (int i = 0; i < AD_STAGES && i < npages; ++i) issue(i, pg_a + i);
+        while (issued < AD_STAGES && issued < npages && pg_a + issued != pg_hi) {
+            issue(issued, pg_a + issued);
+            ++issued;
+        }
+    pdl_wait();
+    pdl_trigger();
+    if (tid == 0)
+        while (issued < AD_STAGES && issued < npages) {
+            issue(issued, pg_a + issued);
+            ++issued;
+        }
 
     // Query fragments: rows = the G heads of this kv head (zero beyond G).
     uint32_t qa[D / 16][4];
@@ -196,28 +231,32 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         }
     }
     __syncthreads();
-    const bool single = (seg0 == seg1);     // the whole sequence was this block's
-    for (int idx = tid; idx < G * D; idx += AD_THREADS) {
-        const int row = idx / D, e = idx - row * D;
+    const bool single = (plan.nseg == 1);   // the whole sequence was this block's
+    constexpr int D4 = D / 4;
+    for (int idx = tid; idx < G * D4; idx += AD_THREADS) {
+        const int row = idx / D4, e = (idx - row * D4) * 4;
         const float M = fmaxf(fmaxf(s_m[0][row], s_m[1][row]), fmaxf(s_m[2][row], s_m[3][row]));
-        float acc = 0.0f, l = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        float l = 0.0f;
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = s_m[w][row];
             const float f = (mw == -INFINITY) ? 0.0f : expf(mw - M);
-            acc += so[((size_t)(w * G + row)) * D + e] * f;
+            const float4 v = *reinterpret_cast<const float4*>(so + ((size_t)(w * G + row)) * D + e);
+            acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
             l += s_l[w][row] * f;
         }
         const size_t head = (size_t)b * nq + (size_t)kvh * G + row;
         if (single) {
-            out[head * D + e] = __float2bfloat16_rn(acc * (1.0f / l));
+            const float inv = 1.0f / l;
+            uint2 w2;
+            w2.x = pack_bf16(acc.x * inv, acc.y * inv);
+            w2.y = pack_bf16(acc.z * inv, acc.w * inv);
+            *reinterpret_cast<uint2*>(out + head * D + e) = w2;
         } else {
             const size_t pi = head * max_segs + seg;
-            part_o[pi * D + e] = acc;
-            if (e == 0) {
-                part_ml[pi * 2] = M;
-                part_ml[pi * 2 + 1] = l;
-            }
+            *reinterpret_cast<float4*>(part_o + pi * D + e) = acc;
+            if (e == 0) *reinterpret_cast<float2*>(part_ml + pi * 2) = make_float2(M, l);
         }
     }
     if (single || counters == nullptr) return;   // done, or a second kernel merges the segments
@@ -229,58 +268,37 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     __syncthreads();
     if (tid == 0) {
         const int ticket = atomicAdd(&counters[b * nkv + kvh], 1);
-        s_last = (ticket == seg1 - seg0);
+        s_last = (ticket == plan.nseg - 1);
         if (s_last) counters[b * nkv + kvh] = 0;
     }
     __syncthreads();
     if (!s_last) return;
     __threadfence();
-    constexpr int MAXC = 64;
-    float* s_f = so + 4 * 16 * D;              // [G][MAXC] factors, then [G] 1/L (past the warp sums)
-    const int nch = seg1 - seg0 + 1;
-    if (nch <= MAXC) {
-        for (int idx = tid; idx < G * nch; idx += AD_THREADS) {
-            const int row = idx / nch, cc = idx - row * nch;
-            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_segs;
-            s_f[row * MAXC + cc] = __ldcg(part_ml + (base + seg0 + cc) * 2);
+    // One pass with a running maximum, so that every load of a thread is in flight at once:
+    // a thread owns four values of one head and reads each segment's (m, l) itself.
+    const int nch = plan.nseg;
+    for (int idx = tid; idx < G * D4; idx += AD_THREADS) {
+        const int row = idx / D4, e = (idx - row * D4) * 4;
+        const size_t head = (size_t)b * nq + (size_t)kvh * G + row;
+        const size_t base = head * max_segs;
+        float M = -INFINITY, L = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll 8
+        for (int cc = 0; cc < nch; ++cc) {
+            const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + cc) * 2));
+            const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + cc) * D + e));
+            const float mn = fmaxf(M, ml.x);
+            const float a = expf(M - mn), f = expf(ml.x - mn);   // a = 0 at the first segment
+            acc.x = acc.x * a + v.x * f; acc.y = acc.y * a + v.y * f;
+            acc.z = acc.z * a + v.z * f; acc.w = acc.w * a + v.w * f;
+            L = L * a + ml.y * f;
+            M = mn;
         }
-        __syncthreads();
-        if (tid < G) {
-            float M = -INFINITY;
-            for (int cc = 0; cc < nch; ++cc) M = fmaxf(M, s_f[tid * MAXC + cc]);
-            const size_t base = ((size_t)b * nq + (size_t)kvh * G + tid) * max_segs;
-            float L = 0.0f;
-            for (int cc = 0; cc < nch; ++cc) {
-                const float f = expf(s_f[tid * MAXC + cc] - M);
-                s_f[tid * MAXC + cc] = f;
-                L += __ldcg(part_ml + (base + seg0 + cc) * 2 + 1) * f;
-            }
-            s_f[G * MAXC + tid] = 1.0f / L;
-        }
-        __syncthreads();
-        for (int idx = tid; idx < G * D; idx += AD_THREADS) {
-            const int row = idx / D, e = idx - row * D;
-            const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_segs + seg0;
-            float acc = 0.0f;
-#pragma unroll 4
-            for (int cc = 0; cc < nch; ++cc) acc += __ldcg(part_o + (base + cc) * D + e) * s_f[row * MAXC + cc];
-            out[((size_t)b * nq + (size_t)kvh * G + row) * D + e] =
-                __float2bfloat16_rn(acc * s_f[G * MAXC + row]);
-        }
-        return;
-    }
-    for (int idx = tid; idx < G * D; idx += AD_THREADS) {
-        const int row = idx / D, e = idx - row * D;
-        const size_t base = ((size_t)b * nq + (size_t)kvh * G + row) * max_segs;
-        float M = -INFINITY;
-        for (int cc = seg0; cc <= seg1; ++cc) M = fmaxf(M, __ldcg(part_ml + (base + cc) * 2));
-        float L = 0.0f, acc = 0.0f;
-        for (int cc = seg0; cc <= seg1; ++cc) {
-            const float f = expf(__ldcg(part_ml + (base + cc) * 2) - M);
-            L += __ldcg(part_ml + (base + cc) * 2 + 1) * f;
-            acc += __ldcg(part_o + (base + cc) * D + e) * f;
-        }
-        out[((size_t)b * nq + (size_t)kvh * G + row) * D + e] = __float2bfloat16_rn(acc * (1.0f / L));
+        const float inv = 1.0f / L;
+        uint2 w2;
+        w2.x = pack_bf16(acc.x * inv, acc.y * inv);
+        w2.y = pack_bf16(acc.z * inv, acc.w * inv);
+        *reinterpret_cast<uint2*>(out + head * D + e) = w2;
     }
 }
 
@@ -289,15 +307,13 @@ template <typename TOut>
 __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
                                            const float* __restrict__ part_ml,
                                            const int* __restrict__ seq_pos, TOut* __restrict__ out,
-                                           int nq, int D, int window, int max_segs) {
+                                           int nq, int D, int window, int max_segs, int seg_pages) {
     pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     const int head = blockIdx.x, b = blockIdx.y;
-    const int p = seq_pos[b];
-    int lo = 0;
-    if (window > 0 && p - window + 1 > 0) lo = p - window + 1;
-    const int c0 = lo / LUMEN_PAGE / AD_SEG_PAGES, c1 = p / LUMEN_PAGE / AD_SEG_PAGES;
-    if (c0 == c1) return;       // a single segment: the first kernel has written the result
+    const SegPlan plan = seg_plan(seq_pos[b], window, seg_pages);
+    if (plan.nseg == 1) return; // a single segment: the first kernel has written the result
+    const int c0 = 0, c1 = plan.nseg - 1;
     const size_t base = ((size_t)b * nq + head) * max_segs;
     float M = -INFINITY;
     for (int c = c0; c <= c1; ++c) M = fmaxf(M, part_ml[(base + c) * 2]);
@@ -313,21 +329,24 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
 }
 
 // Entry point. q, out: bfloat16 [B, nq, D]; caches in the swizzled layout; seq_pos[b] is the
-// position of sequence b's query (its cached length before this token). max_segs: segments
-// (of 8 pages) that the page table can hold, at least ceil(bt_stride / 8). part_o and part_ml
+// position of sequence b's query (its cached length before this token). seg_pages: the most
+// pages a segment has, 1 to 8 (small for few sequences, so that there are blocks enough).
+// max_segs: segments the scratch has room for per (sequence, head): at least
+// min(ceil(bt_stride / seg_pages), 32), the most a sequence is cut into. part_o and part_ml
 // are the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
 // counters: null (a second kernel merges the segments), or B * nkv ints that are zero before
 // the call and zero again after it (the last block of each group merges).
 LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* vcache,
                                 const int* block_table, int bt_stride, const int* seq_pos,
                                 void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
-                                int d, int window, float scale, int max_segs, int* err,
-                                int* counters, cudaStream_t stream) {
+                                int d, int window, float scale, int max_segs, int seg_pages,
+                                int* err, int* counters, cudaStream_t stream) {
     if (B <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || max_segs <= 0)
         return LUMEN_ERR_UNSUPPORTED;
     if (B > 65535 || nkv > 65535) return LUMEN_ERR_UNSUPPORTED;
-    if (AD_SEG_PAGES * max_segs < bt_stride) return LUMEN_ERR_BAD_ARGUMENT;
+    if (seg_pages < 1 || seg_pages > AD_SEG_PAGES) return LUMEN_ERR_BAD_ARGUMENT;
+    if (max_segs < AD_MAX_SEGS && (long long)seg_pages * max_segs < bt_stride) return LUMEN_ERR_BAD_ARGUMENT;
     dim3 grid(max_segs, nkv, B);
     const __nv_bfloat16* qp = (const __nv_bfloat16*)q;
     const __nv_bfloat16* kp = (const __nv_bfloat16*)kcache;
@@ -338,14 +357,14 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
         auto k = attn_decode_kernel<128>;
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         e = lumen_launch(k, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos,
-                         part_o, part_ml, nq, nkv, window, scale, max_segs, err, counters,
+                         part_o, part_ml, nq, nkv, window, scale, max_segs, seg_pages, err, counters,
                          (__nv_bfloat16*)out);
     } else if (d == 64) {
         const int smem = AD_STAGES * 2 * LUMEN_PAGE * 64 * 2;
         auto k = attn_decode_kernel<64>;
         cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         e = lumen_launch(k, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos,
-                         part_o, part_ml, nq, nkv, window, scale, max_segs, err, counters,
+                         part_o, part_ml, nq, nkv, window, scale, max_segs, seg_pages, err, counters,
                          (__nv_bfloat16*)out);
     } else {
         return LUMEN_ERR_UNSUPPORTED;
@@ -356,7 +375,7 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
     dim3 cgrid(nq, B);
     e = lumen_launch(attn_decode_combine_kernel<__nv_bfloat16>, cgrid, dim3(128), 0, stream,
                      (const float*)part_o, (const float*)part_ml, seq_pos, (__nv_bfloat16*)out, nq, d, window,
-                     max_segs);
+                     max_segs, seg_pages);
     if (e != cudaSuccess) return (int)e;
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -420,5 +439,5 @@ LUMEN_API int lumen_attn_decode_noalloc(const void* q, const void* kcache, const
     float* part_o = scratch;
     float* part_ml = scratch + rows * (unsigned long long)d;
     return lumen_attn_decode(q, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml,
-                             B, nq, nkv, d, window, scale, max_segs, err, nullptr, stream);
+                             B, nq, nkv, d, window, scale, max_segs, AD_SEG_PAGES, err, nullptr, stream);
 }

@@ -22,7 +22,8 @@
 // exits.
 //
 // Limits. max_segs is the number of 8-page segments the page table can hold, at least
-// ceil(bt_stride / 8). The call needs B * nq * max_segs * (d + 2) floats. If that is more than
+// ceil(bt_stride / 8); more than 32 is never needed (a sequence of more than 256 pages is cut
+// into 32 longer segments). The call needs B * nq * max_segs * (d + 2) floats. If that is more than
 // the array holds, nothing is launched, a line that names the four numbers goes to stderr, and
 // LUMEN_ERR_SCRATCH_TOO_SMALL is returned. (For 32 query heads of size 128: up to 126 sequences
 // with page tables of 64 pages, i.e. 4,096 positions; 31 sequences with 256 pages.)

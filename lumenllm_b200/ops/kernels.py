@@ -311,6 +311,17 @@ def _decode_counters(device) -> torch.Tensor:
     return t
 
 
+DECODE_MAX_SEGS = 32
+
+
+def decode_segment_pages(B, nkv) -> int:
+    """Pages a decode-attention block walks (unless the sequence is longer than 32 segments):
+    8 when the batch brings blocks enough, fewer for a small batch, so that a short batch is
+    spread over more SMs. A function of the batch and the kv heads only, never of the page
+    table's width, so a wider (padded) table does not change a result."""
+    return max(1, min(8, (B * nkv) // 8))
+
+
 def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     """Split-KV decode attention, bfloat16, swizzled cache, head size 64 or 128, at most
     16 query heads per kv head. q [B, nq, d]; seq_pos int32 [B]: each query's position."""
@@ -324,15 +335,17 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     if seq_pos.numel() < B or block_table.shape[0] < B:
         raise KernelError("attn_decode: metadata shorter than the batch")
     width = block_table.shape[1]
-    max_segs = (width + 7) // 8          # a block walks a segment of 8 pages
+    seg_pages = decode_segment_pages(B, nkv)
+    max_segs = min(-(-width // seg_pages), DECODE_MAX_SEGS)
     out = torch.empty_like(q)
     part_o = torch.empty((B, nq, max_segs, d), dtype=F32, device=q.device)
     part_ml = torch.empty((B, nq, max_segs, 2), dtype=F32, device=q.device)
     counters = _decode_counters(q.device) if B * nkv <= _COUNTERS else None
     f = fn("attn_decode", "lumen_attn_decode",
-           [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, P, P, P])
+           [P, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int, c_int, c_int, c_float, c_int, c_int, P, P, P])
     check(f(ptr(q), ptr(kcache), ptr(vcache), ptr(block_table), block_table.stride(0), ptr(seq_pos),
             ptr(out), ptr(part_o), ptr(part_ml), B, nq, nkv, d, int(window), float(scale), max_segs,
+            seg_pages,
             ptr(error_flag(q.device)), ptr(counters), stream_ptr()), "attn_decode")
     return out
 
