@@ -12,7 +12,7 @@
 //     epilogue (their index mod 4 selects the 32 lanes of tensor memory each may read).
 //
 // Two orientations share the code. With many rows of activations (prompts) A = activations and
-// B = weights, BN = 256. With few rows (decode) the roles are swapped: A = weights, so that the
+// B = weights, BN up to 256 (prompt-sized products go to the two-SM kernel further down). With few rows (decode) the roles are swapped: A = weights, so that the
 // 128-row side of the MMA is filled by weight rows, and B = the activations padded to 16/32/64
 // rows; the product is then a stream over the weights with a deep TMA ring, and k may be split
 // over several tiles so that all SMs pull from HBM. A split writes partial sums [S, M, N] that
@@ -25,6 +25,7 @@
 // lets the other roles run out likewise, frees its tensor memory and returns.
 #include <cuda.h>
 
+#include <cstdlib>
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -86,6 +87,9 @@ __host__ __device__ constexpr uint32_t tc_idesc(int bn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(bn >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
 }
 
+#define TC_TILE_FIXED 200   // fixed part of a tile's time, in columns of tile width (measured: a
+                            // 128-wide tile takes 0.75 of the time of a 256-wide one)
+
 struct TcParams {
     float* out_f32;           // EPI_F32: [S, M, N]
     __nv_bfloat16* out_bf16;  // EPI_SILU: [M, N / 2]
@@ -93,6 +97,7 @@ struct TcParams {
     int rowsA, rowsB;         // rows of the A and of the B operand
     int num_kb;               // 64-wide k blocks in K
     int splits, kb_per_split;
+    int bn;                   // rows of a B tile: BN, or narrower (a multiple of 16) when that fills the SMs better
     int* err;
 };
 
@@ -116,8 +121,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int tilesA = (p.rowsA + TC_BM - 1) / TC_BM, tilesB = (p.rowsB + BN - 1) / BN;
+    const int bn = SWAP ? BN : p.bn;            // the slot in shared memory and the accumulator keep BN
+    const int tilesA = (p.rowsA + TC_BM - 1) / TC_BM, tilesB = (p.rowsB + bn - 1) / bn;
     const int n_items = tilesA * tilesB * p.splits;
+    const uint32_t stage_bytes = A_BYTES + bn * 128;
 
     if (threadIdx.x == 0) {
         for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
@@ -178,31 +185,31 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             while (have && npre < STAGES) {
                 pt[npre] = SWAP ? tb : ta;
                 pk[npre] = kb;
-                mbar_expect_tx(&full[npre], A_BYTES + B_BYTES);
+                mbar_expect_tx(&full[npre], stage_bytes);
                 if (SWAP) tma_load_2d(sA + npre * A_BYTES, &tmA, kb * TC_BK, ta * TC_BM, &full[npre]);
-                else      tma_load_2d(sB + npre * B_BYTES, &tmB, kb * TC_BK, tb * BN, &full[npre]);
+                else      tma_load_2d(sB + npre * B_BYTES, &tmB, kb * TC_BK, tb * bn, &full[npre]);
                 ++npre;
                 advance();
             }
             pdl_wait();
             pdl_trigger();
             for (int i = 0; i < npre; ++i) {
-                if (SWAP) tma_load_2d(sB + i * B_BYTES, &tmB, pk[i] * TC_BK, pt[i] * BN, &full[i]);
+                if (SWAP) tma_load_2d(sB + i * B_BYTES, &tmB, pk[i] * TC_BK, pt[i] * bn, &full[i]);
                 else      tma_load_2d(sA + i * A_BYTES, &tmA, pk[i] * TC_BK, pt[i] * TC_BM, &full[i]);
             }
             for (int it = npre; have && !*abort_flag; ++it, advance()) {
                 const int st = it % STAGES, ph = (it / STAGES) & 1;
                 if (!mbar_wait(&empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
-                mbar_expect_tx(&full[st], A_BYTES + B_BYTES);
+                mbar_expect_tx(&full[st], stage_bytes);
                 tma_load_2d(sA + st * A_BYTES, &tmA, kb * TC_BK, ta * TC_BM, &full[st]);
-                tma_load_2d(sB + st * B_BYTES, &tmB, kb * TC_BK, tb * BN, &full[st]);
+                tma_load_2d(sB + st * B_BYTES, &tmB, kb * TC_BK, tb * bn, &full[st]);
             }
         } else {
             pdl_wait();
         }
     } else if (warp == 1) {
         if (lane == 0) {
-            constexpr uint32_t idesc = tc_idesc(BN);
+            const uint32_t idesc = tc_idesc(bn);
             int it = 0, acc_it = 0;
             for (int item = blockIdx.x; item < n_items && !*abort_flag; item += gridDim.x, ++acc_it) {
                 int ta, tb, s;
@@ -245,10 +252,10 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             const int a = ta * TC_BM + row_in_tile;                 // row of the A operand
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + acc * BN;
 #pragma unroll 1
-            for (int c0 = 0; c0 < BN; c0 += 16) {
+            for (int c0 = 0; c0 < bn; c0 += 16) {
                 float v[16];
                 tc_ld16(taddr0 + c0, v);
-                const int b0 = tb * BN + c0;                        // first row of the B operand
+                const int b0 = tb * bn + c0;                        // first row of the B operand
                 if (EPI == TC_EPI_F32) {
                     float* o = p.out_f32 + (size_t)s * p.M * p.N;
                     if (!SWAP) {            // a = activation row m, b = weight row n
@@ -310,6 +317,279 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(NCOLS) : "memory");
+    }
+}
+
+// ------------------------------------------------------------------- two SMs on one tile
+// For prompts the single-SM kernel above is held back by what it must pull from L2: 48 KB of
+// operands for every 128 x 256 x 64 block of products. Here two CTAs on neighbouring SMs (a
+// cluster of two) share a 256 x 256 tile: each loads its own 128 rows of activations and its own
+// 128 rows of the weight tile (32 KB), and one thread of the even CTA issues
+// tcgen05.mma.cta_group::2, which reads both halves of both operands from the two shared
+// memories and accumulates each CTA's 128 rows in that CTA's own tensor memory. The same
+// products need a third less operand traffic.
+//
+// Protocol (the barriers of both CTAs sit at the same offsets):
+//   full[s]   in the even CTA only: its producer announces 64 KB, and all four TMA loads of a
+//             stage, its own two and the odd CTA's two, complete on it.
+//   empty[s]  in both: tcgen05.commit multicasts the "MMAs have read stage s" signal.
+//   tfull[a]  in both: the same multicast commit once a tile's last MMA is issued.
+//   tempty[a] in the even CTA only: the eight epilogue warps of both CTAs arrive on it.
+// Every wait is bounded in time; when one runs out the CTA raises the error flag and all
+// roles of both CTAs run out in turn and meet at the closing cluster barrier.
+#define TC2_STAGES 6
+#define TC2_TILE_BYTES (TC_BM * 128)      // one 128 x 64 operand tile
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+__device__ __forceinline__ uint64_t global_ns() {
+    uint64_t t;
+    asm volatile("mov.u64 %0, %%globaltimer;" : "=l"(t));
+    return t;
+}
+// Wait with cluster-scope acquire, given up after a quarter of a second.
+__device__ __forceinline__ bool mbar_wait_timed(uint64_t* bar, uint32_t parity) {
+    uint64_t t0 = 0;
+    for (uint32_t it = 0;; ++it) {
+        uint32_t ok;
+        asm volatile(
+            "{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n"
+            " selp.u32 %0, 1, 0, p;\n}"
+            : "=r"(ok)
+            : "r"(smem_u32(bar)), "r"(parity)
+            : "memory");
+        if (ok) return true;
+        if ((it & 255u) == 255u) {
+            const uint64_t now = global_ns();
+            if (t0 == 0) t0 = now;
+            else if (now - t0 > 250000000ull) return false;
+        }
+    }
+}
+// TMA load into this CTA's shared memory that completes on a barrier of either CTA of the pair.
+__device__ __forceinline__ void tma_load_2d_pair(void* dst, const CUtensorMap* map, int c0, int c1,
+                                                 uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes"
+        " [%0], [%1, {%3, %4}], [%2];" ::"r"(smem_u32(dst)),
+        "l"(reinterpret_cast<uint64_t>(map)), "r"(bar_cluster_addr), "r"(c0), "r"(c1)
+        : "memory");
+}
+__device__ __forceinline__ void tc2_commit_both(uint64_t* bar) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;" ::"r"(
+            smem_u32(bar)),
+        "h"((uint16_t)3)
+        : "memory");
+}
+__device__ __forceinline__ void tc2_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                        uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
+        "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// D float32, A and B bfloat16, K-major, M = 256 over the pair, N = 256.
+__host__ __device__ constexpr uint32_t tc2_idesc() {
+    return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+}
+
+template <int EPI>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
+                const TcParams p) {
+    constexpr int STAGES = TC2_STAGES;
+    extern __shared__ __align__(1024) unsigned char smem_raw[];
+    unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
+    unsigned char* sA = smem;
+    unsigned char* sB = smem + STAGES * TC2_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * TC2_TILE_BYTES);
+    uint64_t* full = bars;
+    uint64_t* empty = bars + STAGES;
+    uint64_t* tfull = bars + 2 * STAGES;
+    uint64_t* tempty = bars + 2 * STAGES + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 2 * STAGES + 4);
+    volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const uint32_t rank = cluster_ctarank();          // 0: issues the MMAs; 1: its peer
+    const int pair = blockIdx.x >> 1, n_pairs = gridDim.x >> 1;
+    const int tilesA = (p.rowsA + 255) / 256, tilesB = (p.rowsB + 255) / 256;
+    const int n_items = tilesA * tilesB;
+
+    if (threadIdx.x == 0) {
+        for (int i = 0; i < STAGES; ++i) { mbar_init(&full[i], 1); mbar_init(&empty[i], 1); }
+        for (int i = 0; i < 2; ++i) { mbar_init(&tfull[i], 1); mbar_init(&tempty[i], 8); }
+        *abort_flag = 0;
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+    }
+    if (warp == 1) {
+        // each CTA takes all 512 columns of its own tensor memory, so both get the same address
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
+                     "r"(512)
+                     : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();                   // the peer's barriers exist before anything signals them
+    tc_fence_after();
+    const uint32_t tmem_base = *tmem_slot;
+    if (tmem_base != 0 && threadIdx.x == 0) atomicExch(p.err, 1);   // the pair needs equal addresses
+
+    auto decode = [&](int item, int& ta, int& tb) {
+        ta = item % tilesA;
+        tb = item / tilesA;
+    };
+
+    if (warp == 0) {
+        if (lane == 0) {
+            const uint32_t full0 = map_to_cta(smem_u32(full), 0);     // the even CTA's full[0]
+            int item = pair, ta = 0, tb = 0, kb = 0;
+            bool have = item < n_items;
+            if (have) decode(item, ta, tb);
+            auto advance = [&]() {
+                if (++kb >= p.num_kb) {
+                    kb = 0;
+                    item += n_pairs;
+                    have = item < n_items;
+                    if (have) decode(item, ta, tb);
+                }
+            };
+            // Weights never change: the first ring of weight tiles is requested before the
+            // kernel ahead of this one has finished; activations only after.
+            int npre = 0, pa[STAGES], pk[STAGES];
+            while (have && npre < STAGES) {
+                pa[npre] = ta;
+                pk[npre] = kb;
+                if (rank == 0) mbar_expect_tx(&full[npre], 4 * TC2_TILE_BYTES);
+                tma_load_2d_pair(sB + npre * TC2_TILE_BYTES, &tmB, kb * TC_BK, tb * 256 + (int)rank * 128,
+                                 full0 + npre * 8);
+                ++npre;
+                advance();
+            }
+            pdl_wait();
+            pdl_trigger();
+            for (int i = 0; i < npre; ++i)
+                tma_load_2d_pair(sA + i * TC2_TILE_BYTES, &tmA, pk[i] * TC_BK, pa[i] * 256 + (int)rank * 128,
+                                 full0 + i * 8);
+            for (int it = npre; have && !*abort_flag; ++it, advance()) {
+                const int st = it % STAGES, ph = (it / STAGES) & 1;
+                if (!mbar_wait_timed(&empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
+                if (rank == 0) mbar_expect_tx(&full[st], 4 * TC2_TILE_BYTES);
+                tma_load_2d_pair(sA + st * TC2_TILE_BYTES, &tmA, kb * TC_BK, ta * 256 + (int)rank * 128, full0 + st * 8);
+                tma_load_2d_pair(sB + st * TC2_TILE_BYTES, &tmB, kb * TC_BK, tb * 256 + (int)rank * 128, full0 + st * 8);
+            }
+        } else {
+            pdl_wait();
+        }
+    } else if (warp == 1) {
+        pdl_wait();
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t idesc = tc2_idesc();
+            int it = 0, acc_it = 0;
+            for (int item = pair; item < n_items && !*abort_flag; item += n_pairs, ++acc_it) {
+                const int acc = acc_it & 1, aph = (acc_it >> 1) & 1;
+                if (!mbar_wait_timed(&tempty[acc], aph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem_base + acc * 256;
+                bool ok = true;
+                for (int kb = 0; kb < p.num_kb; ++kb, ++it) {
+                    const int st = it % STAGES, ph = (it / STAGES) & 1;
+                    if (!mbar_wait_timed(&full[st], ph)) { ok = false; break; }
+                    tc_fence_after();
+                    const uint64_t ad = tc_smem_desc(smem_u32(sA + st * TC2_TILE_BYTES));
+                    const uint64_t bd = tc_smem_desc(smem_u32(sB + st * TC2_TILE_BYTES));
+#pragma unroll
+                    for (int k = 0; k < TC_BK / 16; ++k)
+                        tc2_mma(d_tmem, ad + 2 * k, bd + 2 * k, idesc, (kb > 0 || k > 0) ? 1u : 0u);
+                    tc2_commit_both(&empty[st]);
+                }
+                if (!ok) { *abort_flag = 1; atomicExch(p.err, 1); break; }
+                tc2_commit_both(&tfull[acc]);
+            }
+        }
+    } else {
+        pdl_wait();
+        const int q = warp & 3;
+        const int row_in_tile = q * 32 + lane;
+        const uint32_t tempty0 = map_to_cta(smem_u32(tempty), 0);
+        int acc_it = 0;
+        for (int item = pair; item < n_items; item += n_pairs, ++acc_it) {
+            if (__any_sync(0xffffffffu, *abort_flag != 0)) break;
+            int ta, tb;
+            decode(item, ta, tb);
+            const int acc = acc_it & 1, aph = (acc_it >> 1) & 1;
+            bool ok = mbar_wait_timed(&tfull[acc], aph);
+            ok = __all_sync(0xffffffffu, ok);
+            if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(p.err, 1); break; }
+            tc_fence_after();
+            const int a = ta * 256 + (int)rank * 128 + row_in_tile;     // activation row m
+            const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256;
+#pragma unroll 1
+            for (int c0 = 0; c0 < 256; c0 += 16) {
+                float v[16];
+                tc_ld16(taddr0 + c0, v);
+                const int b0 = tb * 256 + c0;                           // weight row n
+                if (a >= p.M || b0 >= p.N) continue;
+                if (EPI == TC_EPI_F32) {
+                    float* dst = p.out_f32 + (size_t)a * p.N + b0;
+                    if ((p.N & 3) == 0 && b0 + 16 <= p.N) {
+#pragma unroll
+                        for (int j = 0; j < 16; j += 4)
+                            *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            if (b0 + j < p.N) dst[j] = v[j];
+                    }
+                } else {            // columns 2i, 2i+1 of this thread are gate_i, up_i
+                    const int half = p.N >> 1;
+                    __nv_bfloat16* dst = p.out_bf16 + (size_t)a * half + (b0 >> 1);
+                    float z[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j) z[j] = v[2 * j] / (1.0f + expf(-v[2 * j])) * v[2 * j + 1];
+                    if ((half & 7) == 0 && b0 + 16 <= p.N) {
+                        uint4 w;
+                        w.x = pack_bf16(z[0], z[1]); w.y = pack_bf16(z[2], z[3]);
+                        w.z = pack_bf16(z[4], z[5]); w.w = pack_bf16(z[6], z[7]);
+                        *reinterpret_cast<uint4*>(dst) = w;
+                    } else {
+#pragma unroll
+                        for (int j = 0; j < 8; ++j)
+                            if (b0 + 2 * j + 1 < p.N) dst[j] = __float2bfloat16_rn(z[j]);
+                    }
+                }
+            }
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) mbar_arrive_cluster(tempty0 + acc * 8);
+        }
+    }
+
+    tc_fence_before();
+    __syncthreads();
+    cluster_sync_all();       // neither CTA leaves while the other may still signal it or read its tiles
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem_base), "r"(512) : "memory");
     }
 }
 
@@ -380,6 +660,31 @@ LUMEN_API int lumen_gemm_tc_splits(int M, int N, int K, int epi) {
     return (num_kb + per - 1) / per;
 }
 
+// Width of the weight tiles for the single-SM kernel in the plain orientation (products too
+// small for the two-SM kernel). Tiles are dealt out to 148 persistent blocks in waves; the
+// cost of a shape is its number of waves times the time of a tile, which is a fixed part (the
+// activation tile every k block needs whatever the width) plus a part that grows with the
+// width. The width with the least cost wins, the wider on a tie: 256 rows x 4,096 run as 128
+// tiles of 64 instead of 32 tiles of 256 (21.7 against 28.6 us). A function of the shape only;
+// every width sums k in the same ascending order.
+static int tc_pick_bn(int M, int N) {
+    const char* forced = std::getenv("LUMEN_TC_BN");
+    if (forced && forced[0]) {
+        const int v = std::atoi(forced);
+        if (v >= 16 && v <= 256 && v % 16 == 0) return v;
+    }
+    const int tilesA = (M + TC_BM - 1) / TC_BM;
+    int best = 256;
+    long best_cost = -1;
+    for (int bn = 256; bn >= 32; bn -= 16) {
+        const long tiles = (long)tilesA * ((N + bn - 1) / bn);
+        const long waves = (tiles + 147) / 148;
+        const long cost = waves * (bn + TC_TILE_FIXED);
+        if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
+    }
+    return best;
+}
+
 template <int BN, int STAGES, bool SWAP, int EPI>
 static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
     constexpr size_t smem = (size_t)STAGES * (TC_BM * 128 + BN * 128) + (2 * STAGES + 4) * 8 + 16 + 1024;
@@ -390,12 +695,54 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
         if (e != cudaSuccess) return (int)e;
         attr_done = true;
     }
-    const int tilesA = (p.rowsA + TC_BM - 1) / TC_BM, tilesB = (p.rowsB + BN - 1) / BN;
+    const int tilesA = (p.rowsA + TC_BM - 1) / TC_BM, tilesB = (p.rowsB + p.bn - 1) / p.bn;
     const int items = tilesA * tilesB * p.splits;
     const int grid = items < sm_count() ? items : sm_count();
     lumen_launch(k, dim3(grid), dim3(TC_THREADS), smem, stream, ma, mb, p);
     LUMEN_LAUNCH_CHECK();
     return 0;
+}
+
+// The two-SM kernel: clusters of two CTAs, one pair per two SMs, persistent over the tiles.
+template <int EPI>
+static int tc2_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
+    constexpr size_t smem = (size_t)TC2_STAGES * 2 * TC2_TILE_BYTES + (2 * TC2_STAGES + 4) * 8 + 16 + 1024;
+    auto k = gemm_tc2_kernel<EPI>;
+    static bool attr_done = false;
+    if (!attr_done) {
+        cudaError_t e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        if (e != cudaSuccess) return (int)e;
+        attr_done = true;
+    }
+    const int items = ((p.rowsA + 255) / 256) * ((p.rowsB + 255) / 256);
+    const int pairs = items < sm_count() / 2 ? items : sm_count() / 2;
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(2 * pairs);
+    cfg.blockDim = dim3(TC_THREADS);
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = 2;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = lumen_pdl_enabled() ? 2 : 1;
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k, ma, mb, p);
+    if (e != cudaSuccess) return (int)e;
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
+// Whether the two-SM kernel takes a prompt-sized product: at least one full wave of 256 x 256
+// tiles for the 74 pairs (fewer tiles are spread better by the single-SM kernel's narrow tiles).
+static bool tc_two_sm(int M, int N) {
+    const char* e = std::getenv("LUMEN_TC_TWO_SM");
+    if (e && e[0] == '0') return false;
+    const long items = (long)((M + 255) / 256) * ((N + 255) / 256);
+    return items >= 74;
 }
 
 // x bfloat16 [M, K]; W bfloat16 [N, K]; K a multiple of 8; both 16-byte aligned.
@@ -422,6 +769,7 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
         const int bn = M <= 16 ? 16 : (M <= 32 ? 32 : 64);
         p.rowsA = N;
         p.rowsB = M;
+        p.bn = bn;
         if ((rc = make_map(&ma, W, N, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, x, M, K, bn))) return rc;
         if (epi == TC_EPI_F32) {
@@ -435,8 +783,16 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
     }
     p.rowsA = M;
     p.rowsB = N;
+    if (tc_two_sm(M, N)) {
+        p.bn = 256;
+        if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
+        if ((rc = make_map(&mb, W, N, K, TC_BM))) return rc;
+        if (epi == TC_EPI_F32) return tc2_launch<TC_EPI_F32>(ma, mb, p, stream);
+        return tc2_launch<TC_EPI_SILU>(ma, mb, p, stream);
+    }
+    p.bn = tc_pick_bn(M, N);
     if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
-    if ((rc = make_map(&mb, W, N, K, 256))) return rc;
+    if ((rc = make_map(&mb, W, N, K, p.bn))) return rc;
     if (epi == TC_EPI_F32) return tc_launch<256, 4, false, TC_EPI_F32>(ma, mb, p, stream);
     return tc_launch<256, 4, false, TC_EPI_SILU>(ma, mb, p, stream);
 }

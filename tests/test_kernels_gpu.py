@@ -392,7 +392,29 @@ def test_gemm_tc_tensor_memory_product(M, N, K_):
         assert torch.equal(one[:, 0], part[:, M // 2])
 
 
-@pytest.mark.parametrize("M,I,H", [(300, 176, 80), (2048, 1536, 256), (40, 176, 80), (3, 12288, 128)])
+@pytest.mark.parametrize("M,N,K_", [(2048, 2560, 320), (1990, 2700, 136), (4100, 1300, 64)])
+def test_gemm_tc_two_sm_product(M, N, K_):
+    """Prompt-sized products run on pairs of SMs (one 256 x 256 tile a pair, both halves of both
+    operands read from the two shared memories): sizes that end inside a tile in every
+    dimension, and rows that do not change when more rows follow them."""
+    from lumenllm_b200.ops import kernels as K
+    g = gen(26)
+    x = torch.randn(M, K_, generator=g).to(BF16)
+    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(BF16)
+    w[7] *= 30.0                      # a row and a column that stand out show a misplaced tile
+    x[M - 3] *= 20.0
+    out = K.gemm_tc(dev(x), dev(w)).cpu()
+    K.check_error_flags()
+    assert out.shape == (1, M, N)
+    ref = x.double() @ w.double().T
+    assert float((out[0].double() - ref).abs().max()) < 1e-4 * max(1.0, float(ref.abs().max()))
+    more = torch.cat([x, torch.randn(300, K_, generator=g).to(BF16)])
+    out2 = K.gemm_tc(dev(more), dev(w)).cpu()
+    assert torch.equal(out2[0, :M], out[0])
+
+
+@pytest.mark.parametrize("M,I,H", [(300, 176, 80), (2048, 1536, 256), (40, 176, 80), (3, 12288, 128),
+                                   (2048, 1300, 80)])
 def test_gemm_tc_with_silu_epilogue_on_interleaved_rows(M, I, H):
     from lumenllm_b200.ops import kernels as K
     g = gen(17)
