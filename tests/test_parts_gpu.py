@@ -1,6 +1,7 @@
 """Each part of a layer alone against its plain formula, and the generality of the
 composition: a layer named twice in the schedule, a layer that reads another layer's cache,
-and a toy mixer with per-sequence state of its own that is registered here, in the test,
+and toy parts (a mixer with per-sequence state of its own, a feed-forward with routing, a
+position encoding with other frequencies and positions) that are registered here, in the test,
 and built and stepped without a change to the library."""
 from dataclasses import replace
 
@@ -280,4 +281,187 @@ def test_a_toy_mixer_with_state_of_its_own(dtype, tiny_models):
             live = [i for i in live if pos[i] < len(seqs[i])]
         for g, r in zip(got, refs):
             assert float((torch.cat(g) - r).abs().max()) < tolerance(name, r), round_
+    eng.cache.check()
+
+
+def _step_whole_tail_and_batch(eng, seqs, cuts):
+    """Logits of every position of each sequence: prompts of cuts[i] tokens in one batch, the
+    rest token by token, shorter sequences ending earlier; slots are freed as they end."""
+    from lumenllm_b200 import StepEntry
+    slots = [eng.alloc_slot() for _ in seqs]
+    lg = eng.step([StepEntry(s, q[:c], list(range(c))) for s, q, c in zip(slots, seqs, cuts)]).cpu()
+    got, at = [], 0
+    for c in cuts:
+        got.append([lg[at:at + c]])
+        at += c
+    pos = list(cuts)
+    live = [i for i in range(len(seqs)) if pos[i] < len(seqs[i])]
+    for i in range(len(seqs)):
+        if i not in live:
+            eng.free_slot(slots[i])
+    while live:
+        lg = eng.step([StepEntry(slots[i], [seqs[i][pos[i]]], [0]) for i in live]).cpu()
+        for k, i in enumerate(live):
+            got[i].append(lg[k:k + 1])
+            pos[i] += 1
+        for i in [i for i in live if pos[i] >= len(seqs[i])]:
+            eng.free_slot(slots[i])
+        live = [i for i in live if pos[i] < len(seqs[i])]
+    return [torch.cat(g) for g in got]
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_a_toy_feed_forward_with_routing(dtype, tiny_models):
+    """A feed-forward that sends every token to ONE of three small experts, chosen by a
+    router in float32, weighted by the margin between the best and the second-best router
+    logit (so that the output is continuous where the choice flips, and a rounding
+    difference cannot turn into a jump): registered here, put into layer 0 of a model whose
+    other layers keep their dense feed-forward, stepped whole, by tokens and in a batch."""
+    from lumenllm_b200 import Engine
+    from lumenllm_b200.config import PartSpec
+    from lumenllm_b200.parts import Linear, register_part
+    H, I, E = 96, 40, 3
+
+    @register_part("ffn", "toy_routed")
+    class Routed:
+        @classmethod
+        def tensors(cls, spec):
+            t = {f"{spec.prefix}.router.weight": ((E, H), "matrix")}
+            for e in range(E):
+                t[f"{spec.prefix}.experts.{e}.up.weight"] = ((I, H), "matrix")
+                t[f"{spec.prefix}.experts.{e}.down.weight"] = ((H, I), "matrix")
+            return t
+
+        def __init__(self, spec, weights, runtime):
+            self.runtime = runtime
+            self.router = weights[f"{spec.prefix}.router.weight"].float()
+            self.up = [Linear(weights[f"{spec.prefix}.experts.{e}.up.weight"], runtime) for e in range(E)]
+            self.down = [Linear(weights[f"{spec.prefix}.experts.{e}.down.weight"], runtime) for e in range(E)]
+
+        def forward(self, y, ctx):
+            logits = y.float() @ self.router.T                       # router in float32
+            top = logits.topk(2, dim=-1)
+            margin = top.values[:, 0] - top.values[:, 1]
+            out = torch.zeros(y.shape, dtype=torch.float32, device=y.device)
+            for e in range(E):                                       # only the chosen expert's rows
+                rows = (top.indices[:, 0] == e).nonzero().flatten()
+                if rows.numel() == 0:
+                    continue
+                z = torch.relu(self.up[e](y[rows].contiguous())).to(self.runtime.dtype)
+                out[rows] = self.down[e](z) * margin[rows, None]
+            return out
+
+    base = spec_of("B")
+    toy = PartSpec("toy_routed", {}, prefix="model.layers.0.moe")
+    layers = list(base.layers)
+    layers[0] = replace(layers[0], ffn=toy)
+    spec = replace(base, layers=tuple(layers))
+    w = gpu_weights(tiny_models["B"])
+    g = torch.Generator().manual_seed(8)
+    # margins of about one: the toy multiplies by them, and must not multiply the rounding of
+    # its bfloat16 inputs beyond what the dense layers around it do
+    w["model.layers.0.moe.router.weight"] = (0.1 * torch.randn(E, H, generator=g)).to(BF16).cuda()
+    for e in range(E):
+        w[f"model.layers.0.moe.experts.{e}.up.weight"] = (0.1 * torch.randn(I, H, generator=g)).to(BF16).cuda()
+        w[f"model.layers.0.moe.experts.{e}.down.weight"] = (0.1 * torch.randn(H, I, generator=g)).to(BF16).cuda()
+    for k in [k for k in w if k.startswith("model.layers.0.mlp.")]:
+        del w[k]                                # the loader's rule: nothing unexpected
+    wf = {k: v.float().cpu() for k, v in w.items()}
+    name = "float32" if dtype == F32 else "bfloat16"
+    eng = Engine(spec, w, dtype=name, max_tokens=2048)
+    cfg = TINY["B"]
+    seen = set()
+
+    def plain(tokens):
+        tokens = torch.tensor(tokens)
+        pos = torch.arange(len(tokens))
+        h = P.embed(tokens, wf["model.embed_tokens.weight"])
+        for i in range(3):
+            if i != 0:
+                h = P.decoder_layer(h, wf, i, cfg, pos)
+                continue
+            p = "model.layers.0."
+            y = P.rms_norm(h, wf[p + "input_layernorm.weight"], 1e-5)
+            r = h + P.attention_block(y, wf, p, cfg, pos, P.layer_window(cfg, 0))
+            y2 = P.rms_norm(r, wf[p + "post_attention_layernorm.weight"], 1e-5)
+            logits = y2 @ wf[p + "moe.router.weight"].T
+            out = torch.zeros_like(y2)
+            for t in range(len(tokens)):
+                order = logits[t].argsort(descending=True)
+                e = int(order[0])
+                seen.add(e)
+                z = torch.relu(wf[p + f"moe.experts.{e}.up.weight"] @ y2[t])
+                out[t] = (wf[p + f"moe.experts.{e}.down.weight"] @ z) * (logits[t, order[0]] - logits[t, order[1]])
+            h = r + out
+        return P.rms_norm(h, wf["model.norm.weight"], 1e-5) @ wf["lm_head.weight"].T
+
+    seqs = seeded_tokens(384, [33, 5, 18], 6)
+    refs = [plain(q) for q in seqs]
+    assert seen == {0, 1, 2}, "the test's tokens must reach every expert"
+    for round_ in range(2):
+        got = _step_whole_tail_and_batch(eng, seqs, [25, 1, 18])
+        for a, r in zip(got, refs):
+            assert float((a - r).abs().max()) < tolerance(name, r), round_
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_a_toy_position_encoding(dtype, tiny_models):
+    """A rotation with other frequencies AND other positions than the library's (every
+    position counts 2.5 steps, base 777): a position part is whatever fills the step's
+    (cos, sin) table. Registered here and used by layer 1 only; layers 0 and 2 keep theirs."""
+    from lumenllm_b200 import Engine
+    from lumenllm_b200.config import PartSpec
+    from lumenllm_b200.parts import register_part
+    STRETCH, BASE = 2.5, 777.0
+
+    @register_part("position", "toy_stretched")
+    class Stretched:
+        @classmethod
+        def tensors(cls, spec):
+            return {}
+
+        def __init__(self, spec, weights, runtime):
+            self.rotary_dim = int(spec.params["head_dim"])
+            i2 = torch.arange(0, self.rotary_dim, 2, dtype=torch.float32)
+            self.inv_freq = (1.0 / (torch.tensor(BASE) ** (i2 / self.rotary_dim))).to(runtime.device)
+
+        def angles(self, ctx):
+            a = (ctx.rope_pos.float() * STRETCH)[:, None] * self.inv_freq[None, :]
+            return torch.stack([torch.cos(a), torch.sin(a)], dim=-1).contiguous()
+
+    cfg = TINY["B"]
+    base = spec_of("B")
+    layers = list(base.layers)
+    d = layers[1].mixer.params["head_dim"]
+    layers[1] = replace(layers[1], mixer=replace(layers[1].mixer, params=dict(
+        layers[1].mixer.params, position=PartSpec("toy_stretched", {"head_dim": d}))))
+    spec = replace(base, layers=tuple(layers))
+    w = gpu_weights(tiny_models["B"])
+    wf = {k: v.float().cpu() for k, v in w.items()}
+    name = "float32" if dtype == F32 else "bfloat16"
+    eng = Engine(spec, w, dtype=name, max_tokens=2048)
+
+    def plain(tokens):
+        tokens = torch.tensor(tokens)
+        pos = torch.arange(len(tokens))
+        h = P.embed(tokens, wf["model.embed_tokens.weight"])
+        for i in range(3):
+            if i != 1:
+                h = P.decoder_layer(h, wf, i, cfg, pos)
+                continue
+            p = "model.layers.1."
+            toy_cfg = dict(cfg, rope_theta=BASE)
+            y = P.rms_norm(h, wf[p + "input_layernorm.weight"], 1e-5)
+            r = h + P.attention_block(y, wf, p, toy_cfg, pos.float() * STRETCH, P.layer_window(cfg, 1))
+            h = r + P.mlp_block(P.rms_norm(r, wf[p + "post_attention_layernorm.weight"], 1e-5), wf, p)
+        return P.rms_norm(h, wf["model.norm.weight"], 1e-5) @ wf["lm_head.weight"].T
+
+    seqs = seeded_tokens(384, [41, 3, 20], 7)
+    refs = [plain(q) for q in seqs]
+    stock = P.forward_logits(cfg, wf, seqs[0])
+    assert float((stock - refs[0]).abs().max()) > 5 * tolerance(name, refs[0]), "the toy must matter"
+    got = _step_whole_tail_and_batch(eng, seqs, [30, 2, 20])
+    for a, r in zip(got, refs):
+        assert float((a - r).abs().max()) < tolerance(name, r)
     eng.cache.check()
