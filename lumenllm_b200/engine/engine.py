@@ -30,6 +30,15 @@ _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
 
 
+class _InFlight:
+    """A launched step: its sampled tokens on the device (valid until the step after the next
+    is launched), the pinned host copy under way, and the event that ends the copy."""
+    __slots__ = ("dev", "host", "done", "n")
+
+    def __init__(self, dev, host, done, n):
+        self.dev, self.host, self.done, self.n = dev, host, done, n
+
+
 class StepError(ValueError):
     """A step was refused before anything ran."""
 
@@ -225,6 +234,38 @@ class Engine:
             entries = [(s, [toks[i]]) for i, (s, _) in enumerate(entries)]
         logits = self.step([StepEntry(s, t, [len(t) - 1]) for s, t in entries])
         return self.sampler.pick(logits, configs, uniforms)
+
+    def launch(self, entries, configs, uniforms, after=None, rows=None) -> "_InFlight":
+        """Starts a step and returns without waiting for it: the generation loop's way to
+        keep the device busy while the host reads the step before. With `after` (the handle
+        of the step before) every entry's token is taken on the device from row rows[k] of
+        that step's sampled tokens; the entries then carry no token of their own."""
+        n = len(entries)
+        if after is not None:
+            fed = after.dev
+            if list(rows) != list(range(fed.shape[0])):
+                idx = torch.tensor(list(rows), dtype=torch.int64).to(self.device, non_blocking=True)
+                fed = fed.index_select(0, idx)
+            dev = self.run_device([(s, [0]) for s, _ in entries], configs, uniforms, tokens_on_device=fed)
+        else:
+            dev = self.run_device(entries, configs, uniforms)
+        # two steps are alive at a time (the one being read and the one run ahead); four
+        # pinned buffers in turn leave room to spare
+        ring = self.__dict__.setdefault("_host_ring", [])
+        if not ring:
+            ring.extend(torch.empty((max(self.cache.max_slots, 1),), dtype=torch.int32).pin_memory()
+                        for _ in range(4))
+        self._launched = getattr(self, "_launched", 0) + 1
+        host = ring[self._launched % len(ring)]
+        host[:n].copy_(dev[:n], non_blocking=True)
+        done = torch.cuda.Event()
+        done.record()
+        return _InFlight(dev[:n], host, done, n)
+
+    def collect(self, handle: "_InFlight") -> List[int]:
+        """The sampled tokens of a launched step, on the host."""
+        handle.done.synchronize()
+        return handle.host[:handle.n].tolist()
 
     def generate(self, requests, eos_token_ids=None, max_batch: int = 64, on_token=None):
         """`requests`: one GenerateRequest or a list. Returns GenerateOutput(s)."""

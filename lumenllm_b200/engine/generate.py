@@ -18,6 +18,18 @@ The loop only decides; it needs a backend with
   alloc_slot() / free_slot(slot),
   run(entries: [(slot, tokens)], configs, uniforms) -> one token per entry
 so that its decisions can be tested without a GPU.
+
+A backend may also offer
+  launch(entries, configs, uniforms, after=None, rows=None) -> handle
+  collect(handle) -> one token per entry
+Then the loop keeps one step in flight: while the host waits for the tokens of step n, the
+device already runs step n + 1, fed on the device with step n's tokens (`after` is step n's
+handle, `rows[k]` the place of entry k's sequence in it; such an entry brings no host token).
+Step n + 1 is launched before step n's tokens are known, so it holds every sequence that
+step n cannot end by length; for a sequence that step n then ends by EOS or a stop token,
+the token of step n + 1 is dropped, and its slot is given back when the step that held it
+has been collected. A sequence's tokens, its uniforms (numbered by its own steps) and
+its finish reason are the same as without the run-ahead.
 """
 from __future__ import annotations
 
@@ -93,6 +105,8 @@ def generate(backend, requests: Sequence[GenerateRequest], eos_token_ids: Sequen
     seeds = [r.sampling.seed if r.sampling.seed is not None else fresh_seed() for r in requests]
     outputs: List[Optional[GenerateOutput]] = [None] * len(requests)
 
+    pipelined = hasattr(backend, "launch") and hasattr(backend, "collect")
+
     for batch in plan_batches(requests, max_batch, token_budget):
         live = []            # request indices still generating
         slot_of, produced, nsteps = {}, {}, {}
@@ -106,41 +120,85 @@ def generate(backend, requests: Sequence[GenerateRequest], eos_token_ids: Sequen
             live.append(i)
         if not live:
             continue
-        feed = {i: list(requests[i].prompt_tokens) for i in live}
-        first = True
-        t_prefill = 0.0
-        while live:
-            entries = [(slot_of[i], feed[i]) for i in live]
-            cfgs = [requests[i].sampling for i in live]
-            us = [uniform(seeds[i], 0, nsteps[i]) for i in live]
-            nxt = backend.run(entries, cfgs, us)
-            if first:
-                t_prefill = clock() - t0
-                first = False
-            still = []
-            for i, tok in zip(live, nxt):
-                tok = int(tok)
-                r = requests[i]
+        t_prefill = [0.0]
+
+        def decide(i, tok):
+            """Books request i's next token; returns its finish reason or None."""
+            tok = int(tok)
+            r = requests[i]
+            reason = None
+            if tok in eos:
+                reason = "eos_token"
+            elif tok in set(r.stop_token_ids):
+                produced[i].append(tok)
+                reason = "stop"
+            else:
+                produced[i].append(tok)
+                if len(produced[i]) >= r.max_tokens:
+                    reason = "length"
+            if on_token is not None and reason != "eos_token":
+                on_token(i, tok)
+            if reason is not None:
+                outputs[i] = GenerateOutput(produced[i], len(r.prompt_tokens), len(produced[i]),
+                                            reason, t_prefill[0], clock() - t0 - t_prefill[0])
+            return reason
+
+        def step_inputs(members):
+            cfgs = [requests[i].sampling for i in members]
+            us = [uniform(seeds[i], 0, nsteps[i]) for i in members]
+            for i in members:
                 nsteps[i] += 1
-                reason = None
-                if tok in eos:
-                    reason = "eos_token"
-                elif tok in set(r.stop_token_ids):
-                    produced[i].append(tok)
-                    reason = "stop"
-                else:
-                    produced[i].append(tok)
-                    if len(produced[i]) >= r.max_tokens:
-                        reason = "length"
-                if on_token is not None and reason != "eos_token":
-                    on_token(i, tok)
-                if reason is None:
-                    feed[i] = [tok]
-                    still.append(i)
-                else:
+            return cfgs, us
+
+        if not pipelined:
+            feed = {i: list(requests[i].prompt_tokens) for i in live}
+            first = True
+            while live:
+                entries = [(slot_of[i], feed[i]) for i in live]
+                cfgs, us = step_inputs(live)
+                nxt = backend.run(entries, cfgs, us)
+                if first:
+                    t_prefill[0] = clock() - t0
+                    first = False
+                still = []
+                for i, tok in zip(live, nxt):
+                    if decide(i, tok) is None:
+                        feed[i] = [int(tok)]
+                        still.append(i)
+                    else:
+                        backend.free_slot(slot_of.pop(i))
+                live = still
+            continue
+
+        # One step in flight ahead of the host.
+        cfgs, us = step_inputs(live)
+        handle = backend.launch([(slot_of[i], list(requests[i].prompt_tokens)) for i in live], cfgs, us)
+        members = list(live)
+        done = set()             # ended, slot still held by a step in flight
+        first = True
+        while members:
+            # who goes on after this step whatever it samples, unless it is EOS or a stop token
+            ahead = [i for i in members
+                     if i not in done and len(produced[i]) + 1 < requests[i].max_tokens]
+            nxt_handle = None
+            if ahead:
+                cfgs, us = step_inputs(ahead)
+                rows = [members.index(i) for i in ahead]
+                nxt_handle = backend.launch([(slot_of[i], None) for i in ahead], cfgs, us,
+                                            after=handle, rows=rows)
+            toks = backend.collect(handle)
+            if first:
+                t_prefill[0] = clock() - t0
+                first = False
+            for i, tok in zip(members, toks):
+                if i in done:                    # ended a step ago; this token was run ahead
+                    done.discard(i)
                     backend.free_slot(slot_of.pop(i))
-                    outputs[i] = GenerateOutput(produced[i], len(r.prompt_tokens),
-                                                len(produced[i]), reason, t_prefill,
-                                                clock() - t0 - t_prefill)
-            live = still
+                    continue
+                if decide(i, tok) is not None:
+                    if i in ahead:
+                        done.add(i)              # the step in flight still writes to its slot
+                    else:
+                        backend.free_slot(slot_of.pop(i))
+            handle, members = nxt_handle, ahead
     return outputs  # type: ignore[return-value]

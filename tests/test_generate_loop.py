@@ -118,3 +118,73 @@ def test_on_token_callback():
     b = Scripted({0: [4, 5, 99]})
     generate(b, [GenerateRequest([1], 9)], eos_token_ids=[99], on_token=lambda i, t: seen.append((i, t)))
     assert seen == [(0, 4), (0, 5)]
+
+
+class ScriptedAhead(Scripted):
+    """The same scripted sequences behind launch / collect: a step's tokens become known
+    only when it is collected, and a step may be fed from the step before it."""
+
+    def __init__(self, scripts, n_slots=8):
+        super().__init__(scripts, n_slots)
+        self.in_flight = 0
+        self.max_in_flight = 0
+        self.freed_while_held = []
+
+    def launch(self, entries, configs, uniforms, after=None, rows=None):
+        fed = []
+        for k, (s, t) in enumerate(entries):
+            assert s in self.held, "a launched step names a slot that was given back"
+            if after is None:
+                fed.append((s, list(t)))
+            else:
+                assert t is None
+                fed.append((s, [after["tokens"][rows[k]]]))
+                assert after["slots"][rows[k]] == s
+        self.calls.append(fed)
+        self.uniforms.append(list(uniforms))
+        toks = []
+        for s, _ in entries:
+            toks.append(self.scripts[self.held[s]][self.count[s]])
+            self.count[s] += 1
+        self.in_flight += 1
+        self.max_in_flight = max(self.max_in_flight, self.in_flight)
+        return {"tokens": toks, "slots": [s for s, _ in entries]}
+
+    def collect(self, handle):
+        self.in_flight -= 1
+        return list(handle["tokens"])
+
+
+def test_run_ahead_gives_the_same_tokens_and_reasons():
+    scripts = {0: [5, 6, 99, 1, 1], 1: [7, 42, 8, 8], 2: [1, 2, 3, 4], 3: [9] * 12}
+    reqs = [GenerateRequest([10, 11, 12], max_tokens=8),
+            GenerateRequest([13], max_tokens=8, stop_token_ids=[42]),
+            GenerateRequest([14, 15], max_tokens=3),
+            GenerateRequest([16], max_tokens=6, sampling=SamplingConfig(temperature=0.5, seed=3))]
+    plain_b, ahead_b = Scripted(scripts), ScriptedAhead(scripts)
+    want = generate(plain_b, reqs, eos_token_ids=[99])
+    got = generate(ahead_b, reqs, eos_token_ids=[99])
+    assert [(o.tokens, o.finish_reason) for o in got] == [(o.tokens, o.finish_reason) for o in want]
+    assert ahead_b.max_in_flight == 2                 # one step ahead, never more
+    assert not ahead_b.held and sorted(ahead_b.free) == list(range(8))
+    # request 2 ends by length: it is in no step after the one that gives its last token
+    assert sum(1 for c in ahead_b.calls for s, _ in c if s == 2) == 3
+    # request 0 ends by EOS at its third token: it was run ahead once more, and that is all
+    assert sum(1 for c in ahead_b.calls for s, _ in c if s == 0) == 4
+    # every sequence saw, step by step, the tokens it produced itself
+    for c in ahead_b.calls[1:]:
+        for s, t in c:
+            assert len(t) == 1
+    # uniforms are numbered by the request's own steps, as without the run-ahead
+    u3 = [u for c, us in zip(ahead_b.calls, ahead_b.uniforms) for (s, _), u in zip(c, us) if s == 3]
+    assert u3[:6] == [uniform(3, 0, k) for k in range(6)]
+
+
+def test_run_ahead_batches_reuse_slots_only_after_their_last_step():
+    scripts = {i: [i + 1, 77] + [i + 1] * 6 for i in range(6)}
+    b = ScriptedAhead(scripts, n_slots=2)
+    reqs = [GenerateRequest([1] * (i + 1), max_tokens=4) for i in range(6)]
+    outs = generate(b, reqs, eos_token_ids=[77], max_batch=2)
+    assert [o.tokens for o in outs] == [[i + 1] for i in range(6)]
+    assert all(o.finish_reason == "eos_token" for o in outs)
+    assert not b.held and b.in_flight == 0
