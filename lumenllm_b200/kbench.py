@@ -6,6 +6,8 @@
     python -m lumenllm_b200.kbench attn_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
     python -m lumenllm_b200.kbench add_rmsnorm --m 2048 --n 4096
     python -m lumenllm_b200.kbench qk_rope --m 2048 --heads 32 --kv-heads 8 --head-dim 128
+    python -m lumenllm_b200.kbench argmax --m 8 --n 151936
+    python -m lumenllm_b200.kbench sample --m 8 --n 151936 [--top-k 50] [--top-p 0.9]
 
 Each run cycles through `--copies` distinct operand sets (more bytes than the L2 holds, so
 that what is timed comes from HBM), times `--reps` passes with CUDA events after a warm-up and
@@ -56,7 +58,10 @@ def _paged(B, length, nkv, d, dev):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="kbench")
     ap.add_argument("kernel", choices=["gemm_tc", "gemm_small", "attn_decode", "attn_prefill",
-                                       "add_rmsnorm", "qk_rope"])
+                                       "add_rmsnorm", "qk_rope", "argmax", "sample"])
+    ap.add_argument("--top-k", type=int, default=0)
+    ap.add_argument("--top-p", type=float, default=1.0)
+    ap.add_argument("--min-p", type=float, default=0.0)
     ap.add_argument("--m", type=int, default=2048)
     ap.add_argument("--n", type=int, default=4096)
     ap.add_argument("--k", type=int, default=4096)
@@ -111,6 +116,16 @@ def main(argv=None):
         fns = [lambda h=h, d=d: K.add_rmsnorm(h, d, w, 1e-6, bf) for h, d in zip(hs, ds)]
         us = _time(fns, a.reps)
         note = f"{a.m * a.n * 14 / us / 1e3:.0f} GB/s"
+    elif a.kernel in ("argmax", "sample"):
+        lgs = [torch.randn(a.m, a.n, device=dev) * 3 for _ in range(a.copies)]
+        if a.kernel == "argmax":
+            fns = [lambda l=l: K.argmax(l) for l in lgs]
+        else:
+            opts = torch.tensor([[0.8, a.top_p, a.min_p, 0.37]] * a.m, dtype=torch.float32, device=dev)
+            tk = torch.full((a.m,), a.top_k, dtype=torch.int32, device=dev)
+            fns = [lambda l=l: K.sample(l, opts, tk) for l in lgs]
+        us = _time(fns, a.reps)
+        note = f"{a.m * a.n * 4 / us / 1e3:.0f} GB/s"
     else:
         nh = a.heads + 2 * a.kv_heads
         xs = [torch.randn(a.m, nh * a.head_dim, device=dev) for _ in range(a.copies)]

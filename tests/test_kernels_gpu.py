@@ -506,3 +506,32 @@ def test_sampler_edges():
     assert got[5] == 2                                        # of 1,2,3 the first two are kept
     lo = _sample_rows(lg[:1], [[1.0, 1.0, 0.0, 0.25]], [2])
     assert lo == [3]
+
+
+def test_sampler_runs_of_equal_logits_and_a_large_vocabulary():
+    """Rows the sampler's quick route must hand to the exact radix route (thousands of equal
+    logits fall into one bin), and the full-size vocabulary, against the plain sampler."""
+    g = gen(31)
+    V = 151936
+    flat = torch.full((4, 6000), 1.0)
+    flat[1, 17] = 3.0
+    flat[2, ::2] = 1.0000001                                  # two keys one ulp apart, 3,000 each
+    flat[3, 100:200] = 2.5
+    opts = [[1.0, 1.0, 0.0, 0.61], [0.7, 0.9, 0.0, 0.95], [1.0, 1.0, 0.0, 0.25], [1.0, 0.5, 0.0, 0.5]]
+    ks = [0, 0, 4000, 150]
+    got = _sample_rows(flat, opts, ks)
+    for r, (tok, o, k) in enumerate(zip(got, opts, ks)):
+        assert tok in _acceptable(flat[r], o[0], k, o[1], o[2], o[3]), (r, tok)
+    big = torch.randn(6, V, generator=g) * 2.5
+    big[:, 7] = big[:, 150000]
+    opts = [[0.8, 1.0, 0.0, 0.3], [1.0, 0.9, 0.0, 0.77], [0.6, 0.95, 0.0, 0.999], [1.0, 1.0, 0.0, 0.5],
+            [1.5, 0.8, 0.0, 0.05], [1.0, 1.0, 0.02, 0.4]]
+    ks = [0, 0, 50, 20, 1000, 0]
+    got = _sample_rows(big, opts, ks)
+    for r, (tok, o, k) in enumerate(zip(got, opts, ks)):
+        assert tok in _acceptable(big[r], o[0], k, o[1], o[2], o[3]), (r, tok)
+    assert _sample_rows(big[2:3], opts[2:3], ks[2:3]) == got[2:3]
+    # the sampler spreads a row over 8, 4, 2 or 1 blocks by the size of the batch: same tokens
+    for copies in (4, 7, 12):                                 # 24, 42 and 72 rows
+        rep = _sample_rows(big.repeat(copies, 1), opts * copies, ks * copies)
+        assert rep == got * copies, copies
