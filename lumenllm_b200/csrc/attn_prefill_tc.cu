@@ -14,8 +14,12 @@
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the reference it
 // was accumulated against (P and the row sum use the same reference, so the result is exact);
 // the rescale is a read-modify-write of the row in tensor memory and is rare after the first
-// pages. K and V tiles arrive through a two-stage ring of bulk asynchronous copies
-// (cp.async.bulk + mbarrier; a page tile is one contiguous block of the cache). Warp 0
+// pages. K and V tiles arrive through two two-stage rings of bulk asynchronous copies
+// (cp.async.bulk + mbarrier; a page tile is one contiguous block of the cache). The rings are
+// separate because their slots come free at different times: a K slot as soon as the S
+// product that read it is done, which is a page ahead of the V slot that the O product of the
+// same page frees; K for page i+2 is therefore on its way two pages early and V more than one,
+// and the latency of the copies stays hidden with two slots each. Warp 0
 // produces, warp 1 allocates tensor memory and issues all MMAs, warps 2..5 are the softmax.
 // A block needs half of an SM's shared memory and half of its tensor memory, so two blocks
 // share an SM and one's softmax runs under the other's products.
@@ -154,9 +158,11 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     unsigned char* sKV = sQ + Q_BYTES;                  // [stage][K tile, V tile]
     unsigned char* sP = sKV + PT_STAGES * 2 * TILE_BYTES;   // one buffer: the product that read it is awaited
     uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
-    uint64_t* kv_full = bars;                  // [stages] tiles have landed
-    uint64_t* kv_empty = bars + PT_STAGES;     // [stages] the PV product has read them
-    uint64_t* s_full = bars + 2 * PT_STAGES;   // [2] S is in tensor memory
+    uint64_t* k_full = bars;                   // [stages] the K tile has landed
+    uint64_t* k_empty = bars + PT_STAGES;      // [stages] the S product has read it
+    uint64_t* v_full = bars + 2 * PT_STAGES;   // [stages] the V tile has landed
+    uint64_t* v_empty = bars + 3 * PT_STAGES;  // [stages] the O product has read it
+    uint64_t* s_full = bars + 4 * PT_STAGES;   // [2] S is in tensor memory
     uint64_t* p_ready = s_full + 2;            // [2] P is in shared memory, O corrected
     uint64_t* pv_done = p_ready + 2;           // [2] the PV product of that page has finished
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
@@ -164,8 +170,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
     const int G = nq / nkv;
     const int TQ = PT_ROWS / G;
-    const int kvh = blockIdx.y;
-    int tile = blockIdx.x, b = 0, qlen = 0;
+    // blocks start in the order of blockIdx.x: tile-major, so that the longest tiles of ALL kv
+    // heads start first and the short ones fill the tail
+    const int kvh = blockIdx.x % nkv;
+    int tile = blockIdx.x / nkv, b = 0, qlen = 0;
     for (; b < B; ++b) {
         qlen = cu_q[b + 1] - cu_q[b];
         const int nt = (qlen + TQ - 1) / TQ;
@@ -188,7 +196,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
 
     if (threadIdx.x == 0) {
-        for (int i = 0; i < PT_STAGES; ++i) { mbar_init(&kv_full[i], 1); mbar_init(&kv_empty[i], 1); }
+        for (int i = 0; i < PT_STAGES; ++i) {
+            mbar_init(&k_full[i], 1); mbar_init(&k_empty[i], 1);
+            mbar_init(&v_full[i], 1); mbar_init(&v_empty[i], 1);
+        }
         for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 4); mbar_init(&pv_done[i], 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -216,14 +227,23 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int it = 0; it < npages && !*abort_flag; ++it) {
-                const int st = it % PT_STAGES, ph = (it / PT_STAGES) & 1;
-                if (!mbar_wait(&kv_empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(err, 1); break; }
-                const size_t off = ((size_t)bt[pg_lo + it] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
-                unsigned char* dst = sKV + st * 2 * TILE_BYTES;
-                mbar_expect_tx(&kv_full[st], 2 * TILE_BYTES);
-                bulk_load(dst, kcache + off, TILE_BYTES, &kv_full[st]);
-                bulk_load(dst + TILE_BYTES, vcache + off, TILE_BYTES, &kv_full[st]);
+            // K runs one page ahead of V: its slot comes free earlier (see above), and this way
+            // no K waits behind a V whose slot is still being read
+            for (int s = 0; s <= npages && !*abort_flag; ++s) {
+                if (s < npages) {
+                    const int st = s % PT_STAGES, ph = (s / PT_STAGES) & 1;
+                    const size_t off = ((size_t)bt[pg_lo + s] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+                    if (!mbar_wait(&k_empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(err, 1); break; }
+                    mbar_expect_tx(&k_full[st], TILE_BYTES);
+                    bulk_load(sKV + st * 2 * TILE_BYTES, kcache + off, TILE_BYTES, &k_full[st]);
+                }
+                if (s >= 1) {
+                    const int it = s - 1, st = it % PT_STAGES, ph = (it / PT_STAGES) & 1;
+                    const size_t off = ((size_t)bt[pg_lo + it] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+                    if (!mbar_wait(&v_empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(err, 1); break; }
+                    mbar_expect_tx(&v_full[st], TILE_BYTES);
+                    bulk_load(sKV + st * 2 * TILE_BYTES + TILE_BYTES, vcache + off, TILE_BYTES, &v_full[st]);
+                }
             }
         }
     } else if (warp == 1) {
@@ -240,9 +260,10 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                     pt_mma(tmem_base + (it & 1) * LUMEN_PAGE, pt_desc(smem_u32(sQ) + aoff, 16),
                            pt_desc(kt + boff, 16), idesc_qk, ks > 0 ? 1u : 0u);
                 }
+                pt_commit(&k_empty[st]);        // the K slot is free once these MMAs have read it
                 pt_commit(&s_full[it & 1]);
             };
-            bool ok = mbar_wait(&kv_full[0], 0);
+            bool ok = mbar_wait(&k_full[0], 0);
             if (ok) {
                 pt_fence_after();
                 issue_qk(0);
@@ -250,20 +271,21 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
             for (int it = 0; ok && it < npages && !*abort_flag; ++it) {
                 if (it + 1 < npages) {
                     const int st1 = (it + 1) % PT_STAGES;
-                    if (!mbar_wait(&kv_full[st1], ((it + 1) / PT_STAGES) & 1)) { ok = false; break; }
+                    if (!mbar_wait(&k_full[st1], ((it + 1) / PT_STAGES) & 1)) { ok = false; break; }
                     pt_fence_after();
                     issue_qk(it + 1);
                 }
+                const int st = it % PT_STAGES;
+                if (!mbar_wait(&v_full[st], (it / PT_STAGES) & 1)) { ok = false; break; }
                 if (!mbar_wait(&p_ready[it & 1], (it >> 1) & 1)) { ok = false; break; }
                 pt_fence_after();
-                const int st = it % PT_STAGES;
                 const uint32_t vt = smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES);
                 const uint32_t pt = smem_u32(sP);
 #pragma unroll
                 for (int kk = 0; kk < LUMEN_PAGE / 16; ++kk)     // 16 keys a step
                     pt_mma(tmem_base + O_COL, pt_desc(pt + kk * 32, 16),
                            pt_desc(vt + kk * (16 * 128), LUMEN_PAGE * 128), idesc_pv, (it > 0 || kk > 0) ? 1u : 0u);
-                pt_commit(&kv_empty[st]);
+                pt_commit(&v_empty[st]);
                 pt_commit(&pv_done[it & 1]);
             }
             if (!ok) { *abort_flag = 1; atomicExch(err, 1); }
@@ -408,8 +430,8 @@ LUMEN_API int lumen_attn_prefill_tc(const void* q, const void* kcache, const voi
                                     cudaStream_t stream) {
     if (B <= 0 || n_tiles <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0) return LUMEN_ERR_UNSUPPORTED;
-    if (nkv > 65535) return LUMEN_ERR_UNSUPPORTED;
-    dim3 grid(n_tiles, nkv);
+    if ((long long)n_tiles * nkv > 2147483647LL) return LUMEN_ERR_UNSUPPORTED;
+    dim3 grid(n_tiles * nkv);
     const float scale_log2 = scale * 1.4426950408889634f;
     const __nv_bfloat16* qp = (const __nv_bfloat16*)q;
     const __nv_bfloat16* kp = (const __nv_bfloat16*)kcache;
