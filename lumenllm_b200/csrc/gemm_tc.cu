@@ -97,6 +97,7 @@ struct TcParams {
     int rowsA, rowsB;         // rows of the A and of the B operand
     int num_kb;               // 64-wide k blocks in K
     int splits, kb_per_split;
+    int tma_out;              // two-SM kernel: the output goes through shared memory and the copy engine
     int bn;                   // rows of a B tile: BN, or narrower (a multiple of 16) when that fills the SMs better
     int* err;
 };
@@ -337,7 +338,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
 //   tempty[a] in the even CTA only: the eight epilogue warps of both CTAs arrive on it.
 // Every wait is bounded in time; when one runs out the CTA raises the error flag and all
 // roles of both CTAs run out in turn and meet at the closing cluster barrier.
-#define TC2_STAGES 6
+#define TC2_STAGES 5
+#define TC2_OUT_BYTES (TC_BM * 128)       // one staged block of output: 128 rows of 128 bytes
 #define TC2_TILE_BYTES (TC_BM * 128)      // one 128 x 64 operand tile
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -404,6 +406,41 @@ __device__ __forceinline__ void tc2_mma(uint32_t d_tmem, uint64_t adesc, uint64_
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
         : "memory");
 }
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, float (&v)[32]) {
+    uint32_t r[32];
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+        "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+          "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+          "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+          "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr));
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Store of a staged [128 rows][128 bytes] block (128-byte swizzle) to the output matrix; rows
+// and columns beyond the matrix are left out by the copy engine.
+__device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
+    asm volatile("cp.async.bulk.tensor.2d.global.shared::cta.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
+__device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
+// True in all 128 epilogue threads if it is true in any of them.
+__device__ __forceinline__ bool epi_any(bool pred) {
+    uint32_t r;
+    asm volatile(
+        "{\n .reg .pred p, q;\n setp.ne.u32 q, %1, 0;\n bar.red.or.pred p, 1, 128, q;\n selp.u32 %0, 1, 0, p;\n}"
+        : "=r"(r)
+        : "r"((uint32_t)pred)
+        : "memory");
+    return r != 0;
+}
+
 // D float32, A and B bfloat16, K-major, M = 256 over the pair, N = 256.
 __host__ __device__ constexpr uint32_t tc2_idesc() {
     return (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
@@ -412,13 +449,14 @@ __host__ __device__ constexpr uint32_t tc2_idesc() {
 template <int EPI>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB,
-                const TcParams p) {
+                const __grid_constant__ CUtensorMap tmC, const TcParams p) {
     constexpr int STAGES = TC2_STAGES;
     extern __shared__ __align__(1024) unsigned char smem_raw[];
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* sA = smem;
     unsigned char* sB = smem + STAGES * TC2_TILE_BYTES;
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sB + STAGES * TC2_TILE_BYTES);
+    unsigned char* sOut = sB + STAGES * TC2_TILE_BYTES;            // two staged output blocks
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + 2 * TC2_OUT_BYTES);
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -439,6 +477,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmA)) : "memory");
         asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmB)) : "memory");
+        asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&tmC)) : "memory");
     }
     if (warp == 1) {
         // each CTA takes all 512 columns of its own tensor memory, so both get the same address
@@ -531,18 +570,73 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
         const uint32_t tempty0 = map_to_cta(smem_u32(tempty), 0);
-        int acc_it = 0;
+        const bool issuer = (warp == 2 && lane == 0);    // hands staged blocks to the copy engine
+        int acc_it = 0, out_it = 0;
         for (int item = pair; item < n_items; item += n_pairs, ++acc_it) {
-            if (__any_sync(0xffffffffu, *abort_flag != 0)) break;
             int ta, tb;
             decode(item, ta, tb);
             const int acc = acc_it & 1, aph = (acc_it >> 1) & 1;
-            bool ok = mbar_wait_timed(&tfull[acc], aph);
-            ok = __all_sync(0xffffffffu, ok);
-            if (!ok) { *abort_flag = 1; if (lane == 0) atomicExch(p.err, 1); break; }
+            const bool ok = mbar_wait_timed(&tfull[acc], aph);
+            // one decision for all four warps: they meet at barriers further down
+            if (epi_any(!ok || *abort_flag != 0)) { *abort_flag = 1; if (lane == 0) atomicExch(p.err, 1); break; }
             tc_fence_after();
-            const int a = ta * 256 + (int)rank * 128 + row_in_tile;     // activation row m
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256;
+            const int row0 = ta * 256 + (int)rank * 128;                // first activation row of this CTA
+            if (p.tma_out) {
+                // Through shared memory: each thread puts 32 columns of its row into a staged
+                // block (128 rows of 128 bytes, 16-byte chunk c of row r at c ^ (r & 7), which
+                // keeps the stores free of bank conflicts); when a block is full one thread hands
+                // it to the copy engine, which writes whole lines and clips at the matrix's edge.
+                // Two blocks alternate, so the next is filled while the last is being read.
+                constexpr int SUBS = (EPI == TC_EPI_F32) ? 1 : 4;       // 32-column loads per staged block
+                unsigned char* myrow0 = sOut + row_in_tile * 128;
+                const uint32_t sw = (uint32_t)(row_in_tile & 7);
+#pragma unroll 1
+                for (int cb = 0; cb < 256 / (32 * SUBS); ++cb, ++out_it) {
+                    unsigned char* blk = sOut + (out_it & 1) * TC2_OUT_BYTES;
+                    unsigned char* myrow = myrow0 + (out_it & 1) * TC2_OUT_BYTES;
+                    if (issuer) asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    epi_bar();                                          // the block's last store has read it
+#pragma unroll
+                    for (int sub = 0; sub < SUBS; ++sub) {
+                        float v[32];
+                        tc_ld32(taddr0 + (cb * SUBS + sub) * 32, v);
+                        if (EPI == TC_EPI_F32) {
+#pragma unroll
+                            for (int j = 0; j < 8; ++j)
+                                *reinterpret_cast<float4*>(myrow + (((uint32_t)j ^ sw) << 4)) =
+                                    make_float4(v[4 * j], v[4 * j + 1], v[4 * j + 2], v[4 * j + 3]);
+                        } else {        // columns 2i, 2i+1 of this thread are gate_i, up_i
+                            float z[16];
+#pragma unroll
+                            for (int j = 0; j < 16; ++j) z[j] = v[2 * j] / (1.0f + expf(-v[2 * j])) * v[2 * j + 1];
+#pragma unroll
+                            for (int h = 0; h < 2; ++h) {
+                                uint4 w;
+                                w.x = pack_bf16(z[8 * h], z[8 * h + 1]); w.y = pack_bf16(z[8 * h + 2], z[8 * h + 3]);
+                                w.z = pack_bf16(z[8 * h + 4], z[8 * h + 5]); w.w = pack_bf16(z[8 * h + 6], z[8 * h + 7]);
+                                *reinterpret_cast<uint4*>(myrow + (((uint32_t)(2 * sub + h) ^ sw) << 4)) = w;
+                            }
+                        }
+                    }
+                    if (cb == 256 / (32 * SUBS) - 1) {                  // the accumulator has been read out
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(tempty0 + acc * 8);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epi_bar();
+                    if (issuer) {
+                        const int col0 = (EPI == TC_EPI_F32) ? tb * 256 + cb * 32 : tb * 128 + cb * 64;
+                        const int ncols = (EPI == TC_EPI_F32) ? p.N : (p.N >> 1);
+                        if (row0 < p.M && col0 < ncols) tma_store_2d(&tmC, col0, row0, blk);
+                        // a group a block, stored or not: the wait above counts groups
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                    }
+                }
+                continue;
+            }
+            const int a = row0 + row_in_tile;                           // activation row m
 #pragma unroll 1
             for (int c0 = 0; c0 < 256; c0 += 16) {
                 float v[16];
@@ -582,6 +676,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0 + acc * 8);
         }
+        if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores have landed
     }
 
     tc_fence_before();
@@ -703,10 +798,28 @@ static int tc_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParam
     return 0;
 }
 
+// Map of the output for the staged store: row-major [rows, cols] of float32 or bfloat16, blocks
+// of 128 rows x 128 bytes, 128-byte swizzle.
+static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool f32) {
+    EncodeTiledFn fn = encode_fn();
+    if (!fn) return LUMEN_ERR_UNSUPPORTED;
+    const int esz = f32 ? 4 : 2;
+    cuuint64_t dims[2] = {(cuuint64_t)cols, (cuuint64_t)rows};
+    cuuint64_t strides[1] = {(cuuint64_t)cols * esz};
+    cuuint32_t box[2] = {(cuuint32_t)(128 / esz), TC_BM};
+    cuuint32_t estr[2] = {1, 1};
+    CUresult r = fn(map, f32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, base, dims,
+                    strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+                    CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    return r == CUDA_SUCCESS ? 0 : LUMEN_ERR_BAD_ARGUMENT;
+}
+
 // The two-SM kernel: clusters of two CTAs, one pair per two SMs, persistent over the tiles.
 template <int EPI>
-static int tc2_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcParams& p, cudaStream_t stream) {
-    constexpr size_t smem = (size_t)TC2_STAGES * 2 * TC2_TILE_BYTES + (2 * TC2_STAGES + 4) * 8 + 16 + 1024;
+static int tc2_launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p,
+                      cudaStream_t stream) {
+    constexpr size_t smem = (size_t)TC2_STAGES * 2 * TC2_TILE_BYTES + 2 * TC2_OUT_BYTES +
+                            (2 * TC2_STAGES + 4) * 8 + 16 + 1024;
     auto k = gemm_tc2_kernel<EPI>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -730,7 +843,7 @@ static int tc2_launch(const CUtensorMap& ma, const CUtensorMap& mb, const TcPara
     attr[1].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = attr;
     cfg.numAttrs = lumen_pdl_enabled() ? 2 : 1;
-    cudaError_t e = cudaLaunchKernelEx(&cfg, k, ma, mb, p);
+    cudaError_t e = cudaLaunchKernelEx(&cfg, k, ma, mb, mc, p);
     if (e != cudaSuccess) return (int)e;
     LUMEN_LAUNCH_CHECK();
     return 0;
@@ -763,6 +876,7 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
     p.splits = lumen_gemm_tc_splits(M, N, K, epi);
     p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
     p.err = err;
+    p.tma_out = 0;
     CUtensorMap ma, mb;
     int rc;
     if (tc_swapped(M)) {
@@ -787,8 +901,14 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
         p.bn = 256;
         if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, W, N, K, TC_BM))) return rc;
-        if (epi == TC_EPI_F32) return tc2_launch<TC_EPI_F32>(ma, mb, p, stream);
-        return tc2_launch<TC_EPI_SILU>(ma, mb, p, stream);
+        // the staged store needs output rows that are multiples of 16 bytes
+        const int out_cols = epi == TC_EPI_F32 ? N : N / 2;
+        const int out_esz = epi == TC_EPI_F32 ? 4 : 2;
+        CUtensorMap mc = ma;
+        p.tma_out = ((out_cols * out_esz) % 16 == 0 && ((uintptr_t)out & 15) == 0) ? 1 : 0;
+        if (p.tma_out && (rc = make_out_map(&mc, out, M, out_cols, epi == TC_EPI_F32))) return rc;
+        if (epi == TC_EPI_F32) return tc2_launch<TC_EPI_F32>(ma, mb, mc, p, stream);
+        return tc2_launch<TC_EPI_SILU>(ma, mb, mc, p, stream);
     }
     p.bn = tc_pick_bn(M, N);
     if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
