@@ -227,7 +227,7 @@ def gemm_tc_splits(M, N, K, silu=False) -> int:
 
 def gemm_tc(x, w, silu_interleaved=False):
     """x @ w.T on the tcgen05 tensor cores. x bfloat16 [M, K], w bfloat16 [N, K], K a
-    multiple of 8. Returns float32 partials [S, M, N] (S = 1 unless M <= 64); or, with
+    multiple of 8. Returns float32 partials [S, M, N] (S = 1 unless M <= 256); or, with
     silu_interleaved (rows of w alternate gate_i, up_i), bfloat16 [M, N/2] = silu(gate)*up."""
     require(x, BF16, "gemm_tc.x")
     require(w, BF16, "gemm_tc.w")

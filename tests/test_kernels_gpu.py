@@ -414,7 +414,7 @@ def test_gemm_tc_two_sm_product(M, N, K_):
 
 
 @pytest.mark.parametrize("M,I,H", [(300, 176, 80), (2048, 1536, 256), (40, 176, 80), (3, 12288, 128),
-                                   (2048, 1300, 80)])
+                                   (2048, 1300, 80), (100, 176, 80), (200, 520, 96)])
 def test_gemm_tc_with_silu_epilogue_on_interleaved_rows(M, I, H):
     from lumenllm_b200.ops import kernels as K
     g = gen(17)
