@@ -738,10 +738,19 @@ static int sm_count() {
 // 56 us for 4,096 x 12,288. Beyond that the activations fill 128-row tiles of their own.
 static bool tc_swapped(int M, int epi) { return M <= 128 || (M <= 256 && epi == TC_EPI_F32); }
 
+static bool tc_two_sm(int M, int N);
+static void tc_plain_plan(int M, int N, int K, int epi, int* bn, int* splits);
+
 // Number of k splits: a function of the weight's shape (and of the orientation) only. For the
 // swapped orientation the split that fills the SMs most evenly is chosen, small splits first.
 LUMEN_API int lumen_gemm_tc_splits(int M, int N, int K, int epi) {
-    if (epi == TC_EPI_SILU || !tc_swapped(M, epi)) return 1;
+    if (epi == TC_EPI_SILU) return 1;
+    if (!tc_swapped(M, epi)) {
+        if (tc_two_sm(M, N)) return 1;
+        int bn, splits;
+        tc_plain_plan(M, N, K, epi, &bn, &splits);
+        return splits;
+    }
     const int num_kb = (K + TC_BK - 1) / TC_BK;
     const int tiles = (N + TC_BM - 1) / TC_BM;
     const int sms = 148;   // fixed, so that the split never depends on the device at hand
@@ -765,12 +774,7 @@ LUMEN_API int lumen_gemm_tc_splits(int M, int N, int K, int epi) {
 // width. The width with the least cost wins, the wider on a tie: 256 rows x 4,096 run as 128
 // tiles of 64 instead of 32 tiles of 256 (21.7 against 28.6 us). A function of the shape only;
 // every width sums k in the same ascending order.
-static int tc_pick_bn(int M, int N) {
-    const char* forced = std::getenv("LUMEN_TC_BN");
-    if (forced && forced[0]) {
-        const int v = std::atoi(forced);
-        if (v >= 16 && v <= 256 && v % 16 == 0) return v;
-    }
+static int tc_pick_bn(int M, int N, long* cost_out) {
     const int tilesA = (M + TC_BM - 1) / TC_BM;
     int best = 256;
     long best_cost = -1;
@@ -780,7 +784,37 @@ static int tc_pick_bn(int M, int N) {
         const long cost = waves * (bn + TC_TILE_FIXED);
         if (best_cost < 0 || cost < best_cost) { best_cost = cost; best = bn; }
     }
+    *cost_out = best_cost;
     return best;
+}
+
+// Tile width and k split of the single-SM kernel in the plain orientation. Besides narrow
+// tiles there is a second way to give every SM work when the tiles are few: full-width tiles
+// with k split in up to four parts (partial sums [S, M, N], float32 output only). In the cost
+// model above a part of a tile costs its share of the tile plus a tenth for the partial sums.
+static void tc_plain_plan(int M, int N, int K, int epi, int* bn, int* splits) {
+    long narrow_cost;
+    *bn = tc_pick_bn(M, N, &narrow_cost);
+    *splits = 1;
+    const char* forced = std::getenv("LUMEN_TC_BN");
+    if (forced && forced[0]) {
+        const int v = std::atoi(forced);
+        if (v >= 16 && v <= 256 && v % 16 == 0) *bn = v;
+        return;
+    }
+    if (epi != TC_EPI_F32) return;
+    const int num_kb = (K + TC_BK - 1) / TC_BK;
+    const long tiles = (long)((M + TC_BM - 1) / TC_BM) * ((N + 255) / 256);
+    int s = (int)(148 / tiles);
+    if (s > 4) s = 4;
+    if (s > num_kb / 8) s = num_kb / 8;
+    if (s < 2) return;
+    const long split_cost = (256 + TC_TILE_FIXED) * 11 / (10 * s);
+    if (split_cost < narrow_cost) {
+        *bn = 256;
+        const int per = (num_kb + s - 1) / s;
+        *splits = (num_kb + per - 1) / per;
+    }
 }
 
 template <int BN, int STAGES, bool SWAP, int EPI>
@@ -917,7 +951,8 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
         if (epi == TC_EPI_F32) return tc2_launch<TC_EPI_F32>(ma, mb, mc, p, stream);
         return tc2_launch<TC_EPI_SILU>(ma, mb, mc, p, stream);
     }
-    p.bn = tc_pick_bn(M, N);
+    tc_plain_plan(M, N, K, epi, &p.bn, &p.splits);
+    p.kb_per_split = (p.num_kb + p.splits - 1) / p.splits;
     if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
     if ((rc = make_map(&mb, W, N, K, p.bn))) return rc;
     if (epi == TC_EPI_F32) return tc_launch<256, 4, false, TC_EPI_F32>(ma, mb, p, stream);
