@@ -35,6 +35,7 @@
 #define TC_THREADS 192
 #define TC_EPI_F32 0
 #define TC_EPI_SILU 1
+#define TC_EPI_ADD 2          // float32, added to what the output holds (two-SM kernel only)
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -430,6 +431,13 @@ __device__ __forceinline__ void tma_store_2d(const CUtensorMap* map, int c0, int
                  "r"(smem_u32(src)), "r"(c0), "r"(c1)
                  : "memory");
 }
+// The same, added to the output's float32 values by the copy engine (one add an element).
+__device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int c0, int c1, const void* src) {
+    asm volatile("cp.reduce.async.bulk.tensor.2d.global.shared::cta.add.tile.bulk_group [%0, {%2, %3}], [%1];" ::"l"(
+                     reinterpret_cast<uint64_t>(map)),
+                 "r"(smem_u32(src)), "r"(c0), "r"(c1)
+                 : "memory");
+}
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 // True in all 128 epilogue threads if it is true in any of them.
 __device__ __forceinline__ bool epi_any(bool pred) {
@@ -589,7 +597,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 // keeps the stores free of bank conflicts); when a block is full one thread hands
                 // it to the copy engine, which writes whole lines and clips at the matrix's edge.
                 // Two blocks alternate, so the next is filled while the last is being read.
-                constexpr int SUBS = (EPI == TC_EPI_F32) ? 1 : 4;       // 32-column loads per staged block
+                constexpr int SUBS = (EPI != TC_EPI_SILU) ? 1 : 4;       // 32-column loads per staged block
                 unsigned char* myrow0 = sOut + row_in_tile * 128;
                 const uint32_t sw = (uint32_t)(row_in_tile & 7);
 #pragma unroll 1
@@ -602,7 +610,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     for (int sub = 0; sub < SUBS; ++sub) {
                         float v[32];
                         tc_ld32(taddr0 + (cb * SUBS + sub) * 32, v);
-                        if (EPI == TC_EPI_F32) {
+                        if (EPI != TC_EPI_SILU) {
 #pragma unroll
                             for (int j = 0; j < 8; ++j)
                                 *reinterpret_cast<float4*>(myrow + (((uint32_t)j ^ sw) << 4)) =
@@ -628,9 +636,12 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
                     epi_bar();
                     if (issuer) {
-                        const int col0 = (EPI == TC_EPI_F32) ? tb * 256 + cb * 32 : tb * 128 + cb * 64;
-                        const int ncols = (EPI == TC_EPI_F32) ? p.N : (p.N >> 1);
-                        if (row0 < p.M && col0 < ncols) tma_store_2d(&tmC, col0, row0, blk);
+                        const int col0 = (EPI != TC_EPI_SILU) ? tb * 256 + cb * 32 : tb * 128 + cb * 64;
+                        const int ncols = (EPI != TC_EPI_SILU) ? p.N : (p.N >> 1);
+                        if (row0 < p.M && col0 < ncols) {
+                            if (EPI == TC_EPI_ADD) tma_reduce_add_2d(&tmC, col0, row0, blk);
+                            else tma_store_2d(&tmC, col0, row0, blk);
+                        }
                         // a group a block, stored or not: the wait above counts groups
                         asm volatile("cp.async.bulk.commit_group;" ::: "memory");
                     }
@@ -895,13 +906,19 @@ static bool tc_two_sm(int M, int N) {
     return items >= 74;
 }
 
+// Whether a product of this shape can be added to its output in place (epi 2): the shapes of
+// the two-SM kernel with output rows that are multiples of 16 bytes.
+LUMEN_API int lumen_gemm_tc_adds(int M, int N) { return (!tc_swapped(M, TC_EPI_F32) && tc_two_sm(M, N) && (N & 3) == 0) ? 1 : 0; }
+
 // x bfloat16 [M, K]; W bfloat16 [N, K]; K a multiple of 8; both 16-byte aligned.
+// epi 2: out float32 [M, N] += x W^T (only where lumen_gemm_tc_adds says so).
 // epi 0: out float32 [S, M, N], S = lumen_gemm_tc_splits(M, N, K, 0).
 // epi 1: W's rows alternate gate_i, up_i; out bfloat16 [M, N / 2] = SiLU(gate) * up.
 LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int N, int K, int epi, int* err,
                             cudaStream_t stream) {
     if (M <= 0 || N <= 0) return 0;
-    if (K <= 0 || (K & 7) || (epi != TC_EPI_F32 && epi != TC_EPI_SILU)) return LUMEN_ERR_UNSUPPORTED;
+    if (K <= 0 || (K & 7) || (epi != TC_EPI_F32 && epi != TC_EPI_SILU && epi != TC_EPI_ADD)) return LUMEN_ERR_UNSUPPORTED;
+    if (epi == TC_EPI_ADD && !lumen_gemm_tc_adds(M, N)) return LUMEN_ERR_UNSUPPORTED;
     if (epi == TC_EPI_SILU && (N & 1)) return LUMEN_ERR_UNSUPPORTED;
     if (((uintptr_t)x & 15) || ((uintptr_t)W & 15)) return LUMEN_ERR_BAD_ARGUMENT;
     TcParams p;
@@ -943,11 +960,12 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
         if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
         if ((rc = make_map(&mb, W, N, K, TC_BM))) return rc;
         // the staged store needs output rows that are multiples of 16 bytes
-        const int out_cols = epi == TC_EPI_F32 ? N : N / 2;
-        const int out_esz = epi == TC_EPI_F32 ? 4 : 2;
+        const int out_cols = epi != TC_EPI_SILU ? N : N / 2;
+        const int out_esz = epi != TC_EPI_SILU ? 4 : 2;
         CUtensorMap mc = ma;
         p.tma_out = ((out_cols * out_esz) % 16 == 0 && ((uintptr_t)out & 15) == 0) ? 1 : 0;
-        if (p.tma_out && (rc = make_out_map(&mc, out, M, out_cols, epi == TC_EPI_F32))) return rc;
+        if (p.tma_out && (rc = make_out_map(&mc, out, M, out_cols, epi != TC_EPI_SILU))) return rc;
+        if (epi == TC_EPI_ADD) return p.tma_out ? tc2_launch<TC_EPI_ADD>(ma, mb, mc, p, stream) : LUMEN_ERR_BAD_ARGUMENT;
         if (epi == TC_EPI_F32) return tc2_launch<TC_EPI_F32>(ma, mb, mc, p, stream);
         return tc2_launch<TC_EPI_SILU>(ma, mb, mc, p, stream);
     }

@@ -31,9 +31,11 @@ def takes_tc(x: torch.Tensor, w: torch.Tensor) -> bool:
     return x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
 
 
-def gemm_bf16(x: torch.Tensor, w: torch.Tensor, split_ok: bool = False) -> torch.Tensor:
+def gemm_bf16(x: torch.Tensor, w: torch.Tensor, split_ok: bool = False, add_to=None):
     """x bfloat16 [M, K], w bfloat16 [N, K] -> float32 [M, N]; with split_ok possibly
-    [S, M, N] partial sums that the consumer adds."""
+    [S, M, N] partial sums that the consumer adds. With add_to (float32 [M, N]) the product
+    may instead be added to it in place, where the kernel for this shape can do that; None
+    is returned then, and the caller has nothing left to add."""
     if x.dtype != torch.bfloat16 or w.dtype != torch.bfloat16:
         raise KernelError(f"gemm_bf16: expected bfloat16 operands, got {x.dtype} and {w.dtype}")
     if not x.is_cuda:
@@ -43,6 +45,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, split_ok: bool = False) -> torch
     if takes_small(x.shape[0], x.shape[1], w.shape[0]):
         part = K.gemm_small(x, w)
     elif takes_tc(x, w):
+        if (add_to is not None and add_to.is_contiguous() and add_to.data_ptr() % 16 == 0
+                and K.gemm_tc_adds(x.shape[0], w.shape[0])):
+            return K.gemm_tc(x, w, add_to=add_to)
         part = K.gemm_tc(x, w)
     else:
         return torch.mm(x, w.t(), out_dtype=torch.float32)

@@ -225,26 +225,41 @@ def gemm_tc_splits(M, N, K, silu=False) -> int:
     return int(f(int(M), int(N), int(K), 1 if silu else 0))
 
 
-def gemm_tc(x, w, silu_interleaved=False):
+def gemm_tc_adds(M, N) -> bool:
+    """Whether gemm_tc can add a product of this shape to a float32 matrix in place."""
+    f = library("gemm_tc").lumen_gemm_tc_adds
+    f.restype = c_int
+    f.argtypes = [c_int, c_int]
+    return bool(f(int(M), int(N)))
+
+
+def gemm_tc(x, w, silu_interleaved=False, add_to=None):
     """x @ w.T on the tcgen05 tensor cores. x bfloat16 [M, K], w bfloat16 [N, K], K a
     multiple of 8. Returns float32 partials [S, M, N] (S = 1 unless M <= 256); or, with
-    silu_interleaved (rows of w alternate gate_i, up_i), bfloat16 [M, N/2] = silu(gate)*up."""
+    silu_interleaved (rows of w alternate gate_i, up_i), bfloat16 [M, N/2] = silu(gate)*up;
+    or, with add_to (float32 [M, N], only where gemm_tc_adds(M, N)), adds the product to it
+    in place (one float32 add an element, by the copy engine) and returns None."""
     require(x, BF16, "gemm_tc.x")
     require(w, BF16, "gemm_tc.w")
     M, K = x.shape
     N, K2 = w.shape
     if K != K2 or K % 8:
         raise KernelError(f"gemm_tc: inner sizes {K} and {K2} must agree and be a multiple of 8")
-    if silu_interleaved:
+    epi = 0
+    if add_to is not None:
+        require(add_to, F32, "gemm_tc.add_to")
+        if silu_interleaved or tuple(add_to.shape) != (M, N) or not gemm_tc_adds(M, N):
+            raise KernelError(f"gemm_tc: a product [{M}, {N}] cannot be added in place")
+        out, epi = add_to, 2
+    elif silu_interleaved:
         if N % 2:
             raise KernelError("gemm_tc: gate/up rows must come in pairs")
-        out = torch.empty((M, N // 2), dtype=BF16, device=x.device)
+        out, epi = torch.empty((M, N // 2), dtype=BF16, device=x.device), 1
     else:
         out = torch.empty((gemm_tc_splits(M, N, K), M, N), dtype=F32, device=x.device)
     f = fn("gemm_tc", "lumen_gemm_tc", [P, P, P, c_int, c_int, c_int, c_int, P, P])
-    check(f(ptr(x), ptr(w), ptr(out), M, N, K, 1 if silu_interleaved else 0,
-            ptr(error_flag(x.device)), stream_ptr()), "gemm_tc")
-    return out
+    check(f(ptr(x), ptr(w), ptr(out), M, N, K, epi, ptr(error_flag(x.device)), stream_ptr()), "gemm_tc")
+    return None if add_to is not None else out
 
 
 def argmax(logits, out=None):

@@ -77,7 +77,9 @@ class GQAttention:
     def state_shape(self):
         return None
 
-    def forward(self, y, ctx, entry):
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, entry, residual=None):
         kc, vc, table = entry.cache()
         writes = entry.writes_cache and not self.shares_cache
         # float32 [N, (nq + 2 nkv) d], possibly as S partial sums
@@ -89,7 +91,7 @@ class GQAttention:
                                  kc if nkv_new else None, vc if nkv_new else None,
                                  self.nq, nkv_new, self.d, self.runtime.dtype, layout=entry.layout)
         out = self.attend(q, kc, vc, table, ctx, entry.layout)
-        return self.o(out.view(-1, self.nq * self.d), split_ok=True)
+        return self.o(out.view(-1, self.nq * self.d), split_ok=True, add_to=residual)
 
     def attend(self, q, kc, vc, table, ctx, layout):
         """Chooses the kernel by the step's shape: the split-KV kernel when every sequence

@@ -30,8 +30,17 @@ class PreNormBlock:
         self.ffn = build_part("ffn", layer_spec.ffn, weights, runtime)
 
     def forward(self, h, pending, ctx, entry):
+        # A part that says `adds_residual` is offered the stream itself: it may add its update
+        # there (a prompt-sized product does so in its epilogue) and return None, or return the
+        # update as any part does. Either way the next norm sees the stream plus what is pending.
         y = self.norm_mixer.forward(h, pending, self.runtime.dtype)
-        a = self.mixer.forward(y, ctx, entry)
+        if getattr(self.mixer, "adds_residual", False):
+            a = self.mixer.forward(y, ctx, entry, residual=h)
+        else:
+            a = self.mixer.forward(y, ctx, entry)
         y2 = self.norm_ffn.forward(h, a, self.runtime.dtype)
-        m = self.ffn.forward(y2, ctx)
+        if getattr(self.ffn, "adds_residual", False):
+            m = self.ffn.forward(y2, ctx, residual=h)
+        else:
+            m = self.ffn.forward(y2, ctx)
         return h, m

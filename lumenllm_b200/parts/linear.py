@@ -28,11 +28,13 @@ class Linear:
         dt = torch.float32 if any(w.dtype == torch.float32 for w in weights) else weights[0].dtype
         return cls(torch.cat([w.to(dt) for w in weights], dim=0), runtime)
 
-    def __call__(self, x: torch.Tensor, split_ok: bool = False) -> torch.Tensor:
+    def __call__(self, x: torch.Tensor, split_ok: bool = False, add_to=None):
         """x [M, in] in the run dtype -> float32 [M, out]; with split_ok the result may
-        come as [S, M, out] partial sums for the next norm to add."""
+        come as [S, M, out] partial sums for the next norm to add. With add_to (the float32
+        residual stream [M, out]) the product may be added to it in place instead (prompt-sized
+        products on the tensor cores do that in their epilogue); the result is None then."""
         if self.f32:
             if x.dtype != torch.float32:
                 x = x.float()
             return K.gemm_f32(x, self.weight)
-        return G.gemm_bf16(x, self.weight, split_ok=split_ok)
+        return G.gemm_bf16(x, self.weight, split_ok=split_ok, add_to=add_to)

@@ -43,11 +43,13 @@ class SwiGLU:
         else:
             self.gate_up = Linear.stacked([g, u], runtime)
 
-    def forward(self, y, ctx):
+    adds_residual = True      # forward takes `residual` and may add its update to it in place
+
+    def forward(self, y, ctx, residual=None):
         if self.interleaved and not self.down.f32:
             z = G.gemm_gate_up_silu(y, self.gate_up.weight)         # many rows: one kernel
             if z is not None:
-                return self.down(z, split_ok=True)
+                return self.down(z, split_ok=True, add_to=residual)
         gu = self.gate_up(y, split_ok=True)        # float32 [N, 2I], possibly S partials
         if not self.down.f32:
             out = G.gemm_down_silu(gu, self.down.weight, self.interleaved)   # few rows

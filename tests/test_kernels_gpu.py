@@ -392,7 +392,7 @@ def test_gemm_tc_tensor_memory_product(M, N, K_):
         assert torch.equal(one[:, 0], part[:, M // 2])
 
 
-@pytest.mark.parametrize("M,N,K_", [(2048, 2560, 320), (1990, 2700, 136), (4100, 1300, 64)])
+@pytest.mark.parametrize("M,N,K_", [(2048, 2560, 320), (1990, 2700, 136), (4100, 1300, 64), (2304, 2052, 72)])
 def test_gemm_tc_two_sm_product(M, N, K_):
     """Prompt-sized products run on pairs of SMs (one 256 x 256 tile a pair, both halves of both
     operands read from the two shared memories): sizes that end inside a tile in every
@@ -411,6 +411,14 @@ def test_gemm_tc_two_sm_product(M, N, K_):
     more = torch.cat([x, torch.randn(300, K_, generator=g).to(BF16)])
     out2 = K.gemm_tc(dev(more), dev(w)).cpu()
     assert torch.equal(out2[0, :M], out[0])
+    # added in place to a float32 matrix (the residual stream): one add an element, exactly
+    # what adding the product afterwards gives
+    if K.gemm_tc_adds(M, N):
+        h = torch.randn(M, N, generator=g)
+        hd = dev(h.clone())
+        assert K.gemm_tc(dev(x), dev(w), add_to=hd) is None
+        K.check_error_flags()
+        assert torch.equal(hd.cpu(), h + out[0])
 
 
 @pytest.mark.parametrize("M,I,H", [(300, 176, 80), (2048, 1536, 256), (40, 176, 80), (3, 12288, 128),
