@@ -291,6 +291,39 @@ def test_seeded_sampling_alone_and_in_a_batch(dtype, plain, tiny_models):
     assert other.tokens != together[0].tokens
 
 
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_one_step_ahead_gives_what_step_by_step_gives(dtype, plain, tiny_models):
+    """The engine offers launch / collect, so generation keeps one step in flight ahead of the
+    host; behind a face that offers `run` alone it waits for every step. Same tokens and
+    reasons either way: sampled requests of unequal lengths, one that meets a stop token, one
+    that meets EOS (its token run ahead is dropped), one that uses its allowance up."""
+    from lumenllm_b200 import EngineConfig, GenerateRequest, SamplingConfig, build
+    from lumenllm_b200.engine.generate import generate
+    cfg, w = plain["B"]
+    built = build(EngineConfig(model_path=str(tiny_models["B"]), dtype=dtype, context_size=256,
+                               max_batch=4))
+    eng = built.engine
+
+    class StepByStep:
+        alloc_slot, free_slot, run = eng.alloc_slot, eng.free_slot, eng.run
+
+    prompts = seeded_tokens(cfg["vocab_size"], [21, 3, 40, 9, 5, 17], 83)
+    probe = generate(StepByStep(), [GenerateRequest(p, 10, SamplingConfig(temperature=0.9, seed=50 + i))
+                                    for i, p in enumerate(prompts)], max_batch=4)
+    eos = [probe[1].tokens[3]]                       # request 1 would produce this as its 4th token
+    stop = [probe[2].tokens[5]]
+    reqs = [GenerateRequest(p, 10 if i != 4 else 2, SamplingConfig(temperature=0.9, seed=50 + i),
+                            stop_token_ids=stop if i == 2 else ())
+            for i, p in enumerate(prompts)]
+    slow = generate(StepByStep(), reqs, eos_token_ids=eos, max_batch=4)
+    fast = built.generate(reqs, eos_token_ids=eos)
+    assert [(o.tokens, o.finish_reason) for o in fast] == [(o.tokens, o.finish_reason) for o in slow]
+    assert slow[1].finish_reason == "eos_token" and slow[2].finish_reason == "stop"
+    assert slow[4].finish_reason == "length" and len(slow[4].tokens) == 2
+    eng.cache.check()
+    assert not eng.cache.slots.held
+
+
 def test_trace_run_program(tmp_path, plain, tiny_models):
     """bin/trace_run as a program: whole prompts of a batch, then single tokens, a request
     that ends earlier, then a second batch on the slots of the first."""
