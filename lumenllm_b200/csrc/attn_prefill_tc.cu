@@ -203,6 +203,16 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         for (int i = 0; i < 2; ++i) { mbar_init(&s_full[i], 1); mbar_init(&p_ready[i], 4); mbar_init(&pv_done[i], 1); }
         *abort_flag = 0;
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // the first tiles are on their way while the block gathers Q: K of pages 0 and 1, V of page 0
+        for (int s = 0; s < 2 && s < npages; ++s) {
+            const size_t off = ((size_t)bt[pg_lo + s] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+            mbar_expect_tx(&k_full[s], TILE_BYTES);
+            bulk_load(sKV + s * 2 * TILE_BYTES, kcache + off, TILE_BYTES, &k_full[s]);
+            if (s == 0) {
+                mbar_expect_tx(&v_full[0], TILE_BYTES);
+                bulk_load(sKV + TILE_BYTES, vcache + off, TILE_BYTES, &v_full[0]);
+            }
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(tmem_slot)),
@@ -229,7 +239,13 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
         if (lane == 0) {
             // K runs one page ahead of V: its slot comes free earlier (see above), and this way
             // no K waits behind a V whose slot is still being read
-            for (int s = 0; s <= npages && !*abort_flag; ++s) {
+            // (steps 0 and 1, but for V of page 1, were taken before the Q gather)
+            if (npages > 1) {
+                const size_t off = ((size_t)bt[pg_lo + 1] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+                mbar_expect_tx(&v_full[1], TILE_BYTES);
+                bulk_load(sKV + 2 * TILE_BYTES + TILE_BYTES, vcache + off, TILE_BYTES, &v_full[1]);
+            }
+            for (int s = 2; s <= npages && !*abort_flag; ++s) {
                 if (s < npages) {
                     const int st = s % PT_STAGES, ph = (s / PT_STAGES) & 1;
                     const size_t off = ((size_t)bt[pg_lo + s] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
@@ -237,7 +253,7 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                     mbar_expect_tx(&k_full[st], TILE_BYTES);
                     bulk_load(sKV + st * 2 * TILE_BYTES, kcache + off, TILE_BYTES, &k_full[st]);
                 }
-                if (s >= 1) {
+                if (s >= 3) {
                     const int it = s - 1, st = it % PT_STAGES, ph = (it / PT_STAGES) & 1;
                     const size_t off = ((size_t)bt[pg_lo + it] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
                     if (!mbar_wait(&v_empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(err, 1); break; }
