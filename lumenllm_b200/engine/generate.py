@@ -120,85 +120,92 @@ def generate(backend, requests: Sequence[GenerateRequest], eos_token_ids: Sequen
             live.append(i)
         if not live:
             continue
-        t_prefill = [0.0]
+        try:
+            t_prefill = [0.0]
 
-        def decide(i, tok):
-            """Books request i's next token; returns its finish reason or None."""
-            tok = int(tok)
-            r = requests[i]
-            reason = None
-            if tok in eos:
-                reason = "eos_token"
-            elif tok in set(r.stop_token_ids):
-                produced[i].append(tok)
-                reason = "stop"
-            else:
-                produced[i].append(tok)
-                if len(produced[i]) >= r.max_tokens:
-                    reason = "length"
-            if on_token is not None and reason != "eos_token":
-                on_token(i, tok)
-            if reason is not None:
-                outputs[i] = GenerateOutput(produced[i], len(r.prompt_tokens), len(produced[i]),
-                                            reason, t_prefill[0], clock() - t0 - t_prefill[0])
-            return reason
+            def decide(i, tok):
+                """Books request i's next token; returns its finish reason or None."""
+                tok = int(tok)
+                r = requests[i]
+                reason = None
+                if tok in eos:
+                    reason = "eos_token"
+                elif tok in set(r.stop_token_ids):
+                    produced[i].append(tok)
+                    reason = "stop"
+                else:
+                    produced[i].append(tok)
+                    if len(produced[i]) >= r.max_tokens:
+                        reason = "length"
+                if on_token is not None and reason != "eos_token":
+                    on_token(i, tok)
+                if reason is not None:
+                    outputs[i] = GenerateOutput(produced[i], len(r.prompt_tokens), len(produced[i]),
+                                                reason, t_prefill[0], clock() - t0 - t_prefill[0])
+                return reason
 
-        def step_inputs(members):
-            cfgs = [requests[i].sampling for i in members]
-            us = [uniform(seeds[i], 0, nsteps[i]) for i in members]
-            for i in members:
-                nsteps[i] += 1
-            return cfgs, us
+            def step_inputs(members):
+                cfgs = [requests[i].sampling for i in members]
+                us = [uniform(seeds[i], 0, nsteps[i]) for i in members]
+                for i in members:
+                    nsteps[i] += 1
+                return cfgs, us
 
-        if not pipelined:
-            feed = {i: list(requests[i].prompt_tokens) for i in live}
+            if not pipelined:
+                feed = {i: list(requests[i].prompt_tokens) for i in live}
+                first = True
+                while live:
+                    entries = [(slot_of[i], feed[i]) for i in live]
+                    cfgs, us = step_inputs(live)
+                    nxt = backend.run(entries, cfgs, us)
+                    if first:
+                        t_prefill[0] = clock() - t0
+                        first = False
+                    still = []
+                    for i, tok in zip(live, nxt):
+                        if decide(i, tok) is None:
+                            feed[i] = [int(tok)]
+                            still.append(i)
+                        else:
+                            backend.free_slot(slot_of.pop(i))
+                    live = still
+                continue
+
+            # One step in flight ahead of the host.
+            cfgs, us = step_inputs(live)
+            handle = backend.launch([(slot_of[i], list(requests[i].prompt_tokens)) for i in live], cfgs, us)
+            members = list(live)
+            done = set()             # ended, slot still held by a step in flight
             first = True
-            while live:
-                entries = [(slot_of[i], feed[i]) for i in live]
-                cfgs, us = step_inputs(live)
-                nxt = backend.run(entries, cfgs, us)
+            while members:
+                # who goes on after this step whatever it samples, unless it is EOS or a stop token
+                ahead = [i for i in members
+                         if i not in done and len(produced[i]) + 1 < requests[i].max_tokens]
+                nxt_handle = None
+                if ahead:
+                    cfgs, us = step_inputs(ahead)
+                    rows = [members.index(i) for i in ahead]
+                    nxt_handle = backend.launch([(slot_of[i], None) for i in ahead], cfgs, us,
+                                                after=handle, rows=rows)
+                toks = backend.collect(handle)
                 if first:
                     t_prefill[0] = clock() - t0
                     first = False
-                still = []
-                for i, tok in zip(live, nxt):
-                    if decide(i, tok) is None:
-                        feed[i] = [int(tok)]
-                        still.append(i)
-                    else:
+                for i, tok in zip(members, toks):
+                    if i in done:                    # ended a step ago; this token was run ahead
+                        done.discard(i)
                         backend.free_slot(slot_of.pop(i))
-                live = still
-            continue
-
-        # One step in flight ahead of the host.
-        cfgs, us = step_inputs(live)
-        handle = backend.launch([(slot_of[i], list(requests[i].prompt_tokens)) for i in live], cfgs, us)
-        members = list(live)
-        done = set()             # ended, slot still held by a step in flight
-        first = True
-        while members:
-            # who goes on after this step whatever it samples, unless it is EOS or a stop token
-            ahead = [i for i in members
-                     if i not in done and len(produced[i]) + 1 < requests[i].max_tokens]
-            nxt_handle = None
-            if ahead:
-                cfgs, us = step_inputs(ahead)
-                rows = [members.index(i) for i in ahead]
-                nxt_handle = backend.launch([(slot_of[i], None) for i in ahead], cfgs, us,
-                                            after=handle, rows=rows)
-            toks = backend.collect(handle)
-            if first:
-                t_prefill[0] = clock() - t0
-                first = False
-            for i, tok in zip(members, toks):
-                if i in done:                    # ended a step ago; this token was run ahead
-                    done.discard(i)
-                    backend.free_slot(slot_of.pop(i))
-                    continue
-                if decide(i, tok) is not None:
-                    if i in ahead:
-                        done.add(i)              # the step in flight still writes to its slot
-                    else:
-                        backend.free_slot(slot_of.pop(i))
-            handle, members = nxt_handle, ahead
+                        continue
+                    if decide(i, tok) is not None:
+                        if i in ahead:
+                            done.add(i)              # the step in flight still writes to its slot
+                        else:
+                            backend.free_slot(slot_of.pop(i))
+                handle, members = nxt_handle, ahead
+        except BaseException:
+            # a step was refused (cache full, bad token) or the caller's callback raised: the
+            # batch's slots go back before the error goes on, so the backend stays usable
+            for i in list(slot_of):
+                backend.free_slot(slot_of.pop(i))
+            raise
     return outputs  # type: ignore[return-value]

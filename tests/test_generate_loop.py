@@ -188,3 +188,25 @@ def test_run_ahead_batches_reuse_slots_only_after_their_last_step():
     assert [o.tokens for o in outs] == [[i + 1] for i in range(6)]
     assert all(o.finish_reason == "eos_token" for o in outs)
     assert not b.held and b.in_flight == 0
+
+
+@pytest.mark.parametrize("ahead", [False, True])
+def test_a_refused_step_gives_the_slots_back(ahead):
+    class Refusing(ScriptedAhead if ahead else Scripted):
+        def _count(self):
+            self.n = getattr(self, "n", 0) + 1
+            if self.n == 3:
+                raise RuntimeError("kv cache context exhausted")
+
+        def run(self, entries, configs, uniforms):
+            self._count()
+            return Scripted.run(self, entries, configs, uniforms)
+
+        def launch(self, entries, configs, uniforms, after=None, rows=None):
+            self._count()
+            return ScriptedAhead.launch(self, entries, configs, uniforms, after=after, rows=rows)
+
+    b = Refusing({0: [1] * 9, 1: [2] * 9}, n_slots=4)
+    with pytest.raises(RuntimeError, match="exhausted"):
+        generate(b, [GenerateRequest([5, 6], max_tokens=8), GenerateRequest([7], max_tokens=8)])
+    assert not b.held and sorted(b.free) == list(range(4))
