@@ -11,7 +11,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
-from .native import KernelError, check, fn, library, ptr, require, stream_ptr
+from .native import KernelError, check, fn, int_fn, library, ptr, require, stream_ptr
 
 P = c_void_p
 F32 = torch.float32
@@ -186,10 +186,7 @@ SMALL_M = 16   # the weight-streaming product takes up to this many rows
 
 
 def gemm_small_splits(N, K) -> int:
-    f = library("gemm_small").lumen_gemm_small_splits
-    f.restype = c_int
-    f.argtypes = [c_int, c_int]
-    return int(f(int(N), int(K)))
+    return int(int_fn("gemm_small", "lumen_gemm_small_splits", [c_int, c_int])(int(N), int(K)))
 
 
 def gemm_small(x, w, silu_gate_up=False, interleaved=False):
@@ -219,18 +216,13 @@ def gemm_small(x, w, silu_gate_up=False, interleaved=False):
 
 
 def gemm_tc_splits(M, N, K, silu=False) -> int:
-    f = library("gemm_tc").lumen_gemm_tc_splits
-    f.restype = c_int
-    f.argtypes = [c_int, c_int, c_int, c_int]
-    return int(f(int(M), int(N), int(K), 1 if silu else 0))
+    return int(int_fn("gemm_tc", "lumen_gemm_tc_splits", [c_int, c_int, c_int, c_int])(
+        int(M), int(N), int(K), 1 if silu else 0))
 
 
 def gemm_tc_adds(M, N) -> bool:
     """Whether gemm_tc can add a product of this shape to a float32 matrix in place."""
-    f = library("gemm_tc").lumen_gemm_tc_adds
-    f.restype = c_int
-    f.argtypes = [c_int, c_int]
-    return bool(f(int(M), int(N)))
+    return bool(int_fn("gemm_tc", "lumen_gemm_tc_adds", [c_int, c_int])(int(M), int(N)))
 
 
 def gemm_tc(x, w, silu_interleaved=False, add_to=None):

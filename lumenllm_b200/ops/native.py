@@ -78,8 +78,22 @@ def check(code: int, what: str) -> None:
     raise KernelError(f"{what}: CUDA error {code}")
 
 
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
 def stream_ptr() -> int:
+    """The current stream of the current device as the raw handle the C entry points take.
+    Asked for at every launch (a capture or a `torch.cuda.stream` block changes it), so it goes
+    the short way where torch offers one: hundreds of launches make a step, and the host's time
+    per launch is what a short prompt waits for."""
+    if _raw_stream is not None:
+        return _raw_stream(torch.cuda.current_device())
     return torch.cuda.current_stream().cuda_stream
+
+
+def int_fn(module: str, name: str, argtypes):
+    """A C function of a module that returns a plain number (no launch, no error code)."""
+    return fn(module, name, argtypes)
 
 
 def ptr(t):
