@@ -388,3 +388,32 @@ def test_serving_kernels_at_real_layer_sizes_agree_with_the_32_bit_path(shape):
     ref, got = outs["float32"], outs["bfloat16"]
     assert torch.isfinite(got).all()
     assert float((got - ref).abs().max()) <= tolerance("bfloat16", ref)
+
+
+def test_a_long_prompt_at_real_layer_sizes_agrees_with_the_32_bit_path():
+    """1,200 prompt tokens through one layer of the 14B shape: the prompt-sized products run on
+    pairs of SMs, the output and down projections add to the residual stream in their epilogue,
+    attention has many tiles per kv head; then a second piece of the prompt and decoded tokens
+    over the cache that this left. Against the true 32-bit path of the same weights."""
+    from lumenllm_b200 import Engine, StepEntry
+    from lumenllm_b200.ops import kernels as K
+    cfg = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=1,
+               hidden_size=5120, num_attention_heads=40, intermediate_size=17408,
+               num_key_value_heads=8, head_dim=128, vocab_size=32000, rope_theta=1000000.0,
+               rms_norm_eps=1e-6, max_position_embeddings=40960, tie_word_embeddings=False)
+    assert K.gemm_tc_adds(1200, 5120)              # the shapes this test is about
+    toks = seeded_tokens(32000, [1500], 6)[0]
+    outs = {}
+    for dtype in ("float32", "bfloat16"):
+        eng = Engine.from_random(cfg, seed=4, std=0.02, norm_jitter=0.1, dtype=dtype, max_tokens=4096)
+        s = eng.alloc_slot()
+        a = eng.step([StepEntry(s, toks[:1200], [0, 599, 1199])])
+        b = eng.step([StepEntry(s, toks[1200:1490], [0, 289])])
+        c = [eng.step([StepEntry(s, [toks[1490 + k]], [0])]) for k in range(3)]
+        outs[dtype] = torch.cat([a, b] + c).float().cpu()
+        del eng
+        torch.cuda.empty_cache()
+    K.check_error_flags()
+    ref, got = outs["float32"], outs["bfloat16"]
+    assert torch.isfinite(got).all()
+    assert float((got - ref).abs().max()) <= tolerance("bfloat16", ref)
