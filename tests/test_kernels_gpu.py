@@ -543,3 +543,31 @@ def test_sampler_runs_of_equal_logits_and_a_large_vocabulary():
     for copies in (4, 7, 12):                                 # 24, 42 and 72 rows
         rep = _sample_rows(big.repeat(copies, 1), opts * copies, ks * copies)
         assert rep == got * copies, copies
+
+
+@pytest.mark.parametrize("V,rows", [(777, 96), (5003, 64), (32000, 40)])
+def test_sampler_with_drawn_settings(V, rows):
+    """Rows, options and uniform numbers drawn from a fixed seed: spreads from flat to peaked,
+    repeated values, some -inf entries, every combination of the filters."""
+    import random
+    rng = random.Random(V)
+    g = gen(40 + V % 7)
+    lg = torch.randn(rows, V, generator=g)
+    opts, ks = [], []
+    for r in range(rows):
+        lg[r] *= rng.choice([0.3, 1.0, 3.0, 8.0])
+        if rng.random() < 0.4:
+            lg[r, torch.randint(0, V, (V // 10,), generator=g)] = float("-inf")
+        if rng.random() < 0.4:
+            src = torch.randint(0, V, (V // 20,), generator=g)
+            lg[r, torch.randint(0, V, (V // 20,), generator=g)] = lg[r, src]      # repeated values
+        t = rng.choice([0.3, 0.7, 1.0, 1.6])
+        k = rng.choice([0, 0, 2, 7, 50, 300])
+        p = rng.choice([1.0, 1.0, 0.99, 0.9, 0.5])
+        m = rng.choice([0.0, 0.0, 0.0, 0.02, 0.2])
+        opts.append([t, p, m, rng.random()])
+        ks.append(k)
+    got = _sample_rows(lg, opts, ks)
+    for r, (tok, o, k) in enumerate(zip(got, opts, ks)):
+        ok = _acceptable(lg[r], o[0], k, o[1], o[2], o[3])
+        assert tok in ok, (r, o, k, tok, ok)
