@@ -571,3 +571,31 @@ def test_sampler_with_drawn_settings(V, rows):
     for r, (tok, o, k) in enumerate(zip(got, opts, ks)):
         ok = _acceptable(lg[r], o[0], k, o[1], o[2], o[3])
         assert tok in ok, (r, o, k, tok, ok)
+
+
+def test_products_of_drawn_shapes_through_the_router():
+    """Shapes drawn from a fixed seed across every regime of the product's routing (streaming
+    few-row kernel, weight-streaming tcgen05 orientation with k split, single-SM tiles with
+    narrow widths or k split, two SMs a tile with staged stores, the library where a row is
+    no multiple of 16 bytes): all against the double-precision product."""
+    import random
+    from lumenllm_b200.ops import gemm as G
+    rng = random.Random(7)
+    g = gen(51)
+    shapes = []
+    for lo, hi in [(1, 16), (17, 64), (65, 128), (129, 256), (257, 700), (701, 1400), (1401, 2600)]:
+        for _ in range(4):
+            M = rng.randint(lo, hi)
+            N = rng.choice([rng.randint(8, 300), rng.randint(300, 3000), 4 * rng.randint(75, 1600)])
+            Kd = rng.choice([8 * rng.randint(1, 40), 8 * rng.randint(40, 400), 4 * rng.randint(3, 200) + 2])
+            shapes.append((M, N, Kd))
+    shapes += [(2304, 5120, 264), (1536, 12288, 136)]          # two SMs a tile, ragged k
+    for M, N, Kd in shapes:
+        x = torch.randn(M, Kd, generator=g).to(BF16)
+        w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(BF16)
+        out = G.gemm_bf16(dev(x), dev(w)).cpu()
+        ref = x.double() @ w.double().T
+        err = float((out.double() - ref).abs().max())
+        assert out.shape == (M, N) and err < 2e-4 * max(1.0, float(ref.abs().max())), (M, N, Kd, err)
+    from lumenllm_b200.ops import kernels as K
+    K.check_error_flags()
