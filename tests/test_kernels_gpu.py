@@ -599,3 +599,43 @@ def test_products_of_drawn_shapes_through_the_router():
         assert out.shape == (M, N) and err < 2e-4 * max(1.0, float(ref.abs().max())), (M, N, Kd, err)
     from lumenllm_b200.ops import kernels as K
     K.check_error_flags()
+
+
+@pytest.mark.parametrize("seed", range(6))
+def test_fast_attention_kernels_with_drawn_batches(seed):
+    """Batches drawn from a fixed seed for the three fast attention kernels: group sizes 1 to
+    8, head size 64 or 128, a window or none, decode batches of 1 to 40 sequences (which changes
+    how a sequence is cut into segments) with up to 3,000 cached keys, prompts of 1 to 400
+    tokens on cached prefixes of any length."""
+    import random
+    from lumenllm_b200.ops import kernels as K
+    rng = random.Random(300 + seed)
+    d = rng.choice([64, 128])
+    nkv = rng.choice([1, 2, 4])
+    nq = nkv * rng.choice([1, 2, 4, 5, 8])
+    window = rng.choice([0, 0, rng.randint(3, 700)])
+    # decode
+    B = rng.choice([1, 2, 3, 9, 17, 40])
+    starts = [rng.choice([0, rng.randint(1, 200), rng.randint(200, 3000)]) for _ in range(B)]
+    lens = [1] * B
+    n_pages = sum((s + 64) // 64 for s in starts) + 8
+    table, kc, vc, ks, vs, qs = _attn_case(lens, starts, nq, nkv, d, BF16, window, 70 + seed, n_pages=n_pages)
+    out = K.attn_decode(dev(torch.cat(qs).to(BF16)), dev(to_sw128(kc.to(BF16))), dev(to_sw128(vc.to(BF16))),
+                        dev(table), dev(torch.tensor(starts, dtype=I32)), window, d ** -0.5).cpu().float()
+    K.check_error_flags()
+    ref = _attn_ref(qs, ks, vs, lens, starts, window, BF16)
+    assert float((out - ref).abs().max()) < 2 ** -6, ("decode", seed, B, nq, nkv, d, window)
+    # prompts
+    B = rng.randint(1, 5)
+    lens = [rng.choice([1, rng.randint(2, 60), rng.randint(60, 400)]) for _ in range(B)]
+    starts = [rng.choice([0, 0, rng.randint(1, 700)]) for _ in range(B)]
+    n_pages = sum((s + n + 63) // 64 for s, n in zip(starts, lens)) + 8
+    table, kc, vc, ks, vs, qs = _attn_case(lens, starts, nq, nkv, d, BF16, window, 90 + seed, n_pages=n_pages)
+    cu = torch.tensor([0] + list(torch.tensor(lens).cumsum(0)), dtype=I32)
+    ref = _attn_ref(qs, ks, vs, lens, starts, window, BF16)
+    for tensor_memory in (True, False):
+        out = K.attn_prefill(dev(torch.cat(qs).to(BF16)), dev(to_sw128(kc.to(BF16))), dev(to_sw128(vc.to(BF16))),
+                             dev(table), dev(cu), dev(torch.tensor(starts, dtype=I32)), lens, window,
+                             d ** -0.5, tensor_memory=tensor_memory).cpu().float()
+        K.check_error_flags()
+        assert float((out - ref).abs().max()) < 2 ** -6, ("prefill", tensor_memory, seed, lens, starts, nq, nkv, d, window)
