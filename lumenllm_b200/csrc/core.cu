@@ -75,23 +75,37 @@ __global__ void __launch_bounds__(1024)
 add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
                    const float* __restrict__ w, float eps, TOut* __restrict__ y,
                    const int* __restrict__ rows, int H, int write_h) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
-    pdl_trigger();
     extern __shared__ __align__(16) float xs[];  // H floats
     __shared__ float red[32];
     const int b = blockIdx.x;
+    // The norm's weight never changes: a thread whose share of the row is one group of four
+    // values (the few-row launch: one thread a group) has it in registers before the kernel
+    // ahead has finished, and the row's own chain is loads -> sum -> scale -> store.
+    const bool one_group = (H & 3) == 0 && (int)blockDim.x * 4 >= H;
+    float4 g_early = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (one_group && (int)threadIdx.x * 4 < H) g_early = load4(w + threadIdx.x * 4);
+    pdl_wait();      // nothing else of this kernel touches global memory before this
+    pdl_trigger();
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
     const float* dr = delta + (size_t)r * H;
     float ss = 0.0f;
+    float4 x_mine = make_float4(0.f, 0.f, 0.f, 0.f);      // one_group: the thread's values stay in registers
     if ((H & 3) == 0) {
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
             float4 x = load4(hr + i);
-            for (int s = 0; s < S; ++s) {
-                const float4 d = load4(dr + (size_t)s * delta_stride + i);
-                x.x += d.x; x.y += d.y; x.z += d.z; x.w += d.w;
+            // the partial sums are added in rising order; their loads go out eight at a time
+            for (int s0 = 0; s0 < S; s0 += 8) {
+                float4 d[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (s0 + j < S) d[j] = load4(dr + (size_t)(s0 + j) * delta_stride + i);
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    if (s0 + j < S) { x.x += d[j].x; x.y += d[j].y; x.z += d[j].z; x.w += d[j].w; }
             }
-            *reinterpret_cast<float4*>(xs + i) = x;
+            if (one_group) x_mine = x;
+            else *reinterpret_cast<float4*>(xs + i) = x;
             if (write_h && S > 0) *reinterpret_cast<float4*>(hr + i) = x;
             ss += x.x * x.x;
             ss += x.y * x.y;
@@ -112,8 +126,8 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S
     TOut* yr = y + (size_t)b * H;
     if ((H & 3) == 0) {
         for (int i = threadIdx.x * 4; i < H; i += blockDim.x * 4) {
-            const float4 x = *reinterpret_cast<const float4*>(xs + i);
-            const float4 g = load4(w + i);
+            const float4 x = one_group ? x_mine : *reinterpret_cast<const float4*>(xs + i);
+            const float4 g = one_group ? g_early : load4(w + i);
             Pack4<TOut>::store(yr + i, x.x * scale * g.x, x.y * scale * g.y, x.z * scale * g.z,
                                x.w * scale * g.w);
         }
@@ -163,7 +177,32 @@ __global__ void silu_mul_kernel(const float* __restrict__ gu, int S, size_t spli
     pdl_trigger();
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long step = (long long)gridDim.x * blockDim.x;
-    if (interleaved) {
+    if (interleaved && (I & 3) == 0) {
+        // four (gate, up) pairs a thread: 32 bytes in, 8 out; the partial sums' loads go out
+        // together and are added in rising order
+        const long long total4 = total >> 2;
+        const int I4 = I >> 2;
+        for (; idx < total4; idx += step) {
+            const long long n = idx / I4;
+            const int i = (int)(idx - n * I4) * 4;
+            const float* gp = gu + n * 2 * I + 2 * i;
+            float4 a = load4(gp), b = load4(gp + 4);
+            for (int s0 = 1; s0 < S; s0 += 4) {
+                float4 a2[4], b2[4];
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (s0 + j < S) { a2[j] = load4(gp + (s0 + j) * split_stride); b2[j] = load4(gp + (s0 + j) * split_stride + 4); }
+#pragma unroll
+                for (int j = 0; j < 4; ++j)
+                    if (s0 + j < S) {
+                        a.x += a2[j].x; a.y += a2[j].y; a.z += a2[j].z; a.w += a2[j].w;
+                        b.x += b2[j].x; b.y += b2[j].y; b.z += b2[j].z; b.w += b2[j].w;
+                    }
+            }
+            Pack4<TOut>::store(z + n * I + i, a.x / (1.0f + expf(-a.x)) * a.y, a.z / (1.0f + expf(-a.z)) * a.w,
+                               b.x / (1.0f + expf(-b.x)) * b.y, b.z / (1.0f + expf(-b.z)) * b.w);
+        }
+    } else if (interleaved) {
         for (; idx < total; idx += step) {
             const long long n = idx / I;
             const int i = (int)(idx - n * I);
@@ -211,7 +250,7 @@ LUMEN_API int lumen_silu_mul(const float* gu, int n_splits, void* z, int z_is_bf
     if (I <= 0 || n_splits < 1) return LUMEN_ERR_BAD_ARGUMENT;
     const long long total = (long long)N * I;
     const size_t stride = (size_t)N * 2 * I;
-    long long blocks = ((interleaved ? total : total / 4) + 255) / 256;
+    long long blocks = (((I & 3) ? total : total / 4) + 255) / 256;
     if (blocks > 148 * 16) blocks = 148 * 16;
     if (blocks < 1) blocks = 1;
     if (z_is_bf16)
@@ -343,9 +382,14 @@ qk_norm_rope_store_d128_kernel(const float* __restrict__ qkv, int S, size_t spli
     if (head >= nheads) return;
     const float* src = qkv + ((size_t)n * nheads + head) * d + 4 * lane;
     float4 v = load4(src);
-    for (int s = 1; s < S; ++s) {
-        const float4 v2 = load4(src + s * split_stride);
-        v.x += v2.x; v.y += v2.y; v.z += v2.z; v.w += v2.w;
+    for (int s0 = 1; s0 < S; s0 += 8) {       // the partial sums' loads go out together, added in rising order
+        float4 v2[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (s0 + j < S) v2[j] = load4(src + (size_t)(s0 + j) * split_stride);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (s0 + j < S) { v.x += v2[j].x; v.y += v2[j].y; v.z += v2[j].z; v.w += v2[j].w; }
     }
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
