@@ -15,6 +15,7 @@
 // The k range is split over blockIdx.y (N alone seldom gives enough blocks to fill 148 SMs);
 // each split writes its own partial [S, M, N], and the consumer adds the S partials in rising
 // order. S depends on (N, K) only, never on M, so a row's result is the same in any batch.
+#include <type_traits>
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -121,23 +122,31 @@ gemm_small_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ 
     const __nv_bfloat16* w1 = W + (size_t)(ok1 ? r1 : 0) * K + k0 + 8 * t;
     const int nchunks = kpad >> 6;
     const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
-    uint4 a[GS_UNROLL][4];
+    // The loads in flight are held in two halves that take turns: while one half's values feed
+    // the tensor cores, the other half's loads are still on their way, and a half is requested
+    // again as soon as it has been used, so the stream over the weights never pauses.
+    constexpr int HALF = GS_UNROLL / 2;
+    uint4 a[2][HALF][4];
     // a chunk's two halves: k in [kc + 8t, +8) and [kc + 32 + 8t, +8)
-    auto load_group = [&](int cb) {
+    auto load_half = [&](auto hsel, int cb) {
+        constexpr int h = decltype(hsel)::value;
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
+        for (int u = 0; u < HALF; ++u) {
             const int kc = (cb + u) << 6;
             const bool in_lo = (cb + u) < nchunks && kc + 8 * t + 8 <= klen;
             const bool in_hi = (cb + u) < nchunks && kc + 32 + 8 * t + 8 <= klen;
-            a[u][0] = (ok0 && in_lo) ? ldg_stream(w0 + kc) : zero;
-            a[u][1] = (ok1 && in_lo) ? ldg_stream(w1 + kc) : zero;
-            a[u][2] = (ok0 && in_hi) ? ldg_stream(w0 + kc + 32) : zero;
-            a[u][3] = (ok1 && in_hi) ? ldg_stream(w1 + kc + 32) : zero;
+            a[h][u][0] = (ok0 && in_lo) ? ldg_stream(w0 + kc) : zero;
+            a[h][u][1] = (ok1 && in_lo) ? ldg_stream(w1 + kc) : zero;
+            a[h][u][2] = (ok0 && in_hi) ? ldg_stream(w0 + kc + 32) : zero;
+            a[h][u][3] = (ok1 && in_hi) ? ldg_stream(w1 + kc + 32) : zero;
         }
     };
+    using H0 = std::integral_constant<int, 0>;
+    using H1 = std::integral_constant<int, 1>;
     // Weights never change: the first loads are on their way before the kernel ahead of this
     // one in the stream has finished. Activations and outputs come after the wait.
-    load_group(0);
+    load_half(H0{}, 0);
+    load_half(H1{}, HALF);
     pdl_wait();
     pdl_trigger();
 
@@ -154,10 +163,10 @@ gemm_small_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ 
     float c[NT][4];
 #pragma unroll
     for (int nt = 0; nt < NT; ++nt) c[nt][0] = c[nt][1] = c[nt][2] = c[nt][3] = 0.0f;
-    for (int cb = 0; cb < nchunks; cb += GS_UNROLL) {
-        if (cb > 0) load_group(cb);
+    auto use_half = [&](auto hsel, int cb) {
+        constexpr int h = decltype(hsel)::value;
 #pragma unroll
-        for (int u = 0; u < GS_UNROLL; ++u) {
+        for (int u = 0; u < HALF; ++u) {
             if (cb + u >= nchunks) break;
             const int kc = (cb + u) << 6;
 #pragma unroll
@@ -170,12 +179,18 @@ gemm_small_kernel(const void* __restrict__ x, const __nv_bfloat16* __restrict__ 
                 for (int j = 0; j < 4; ++j) {
                     // mma k-slots (2t, 2t+1) carry k = kc + 8t + 2j (+1); slots (2t+8, 2t+9)
                     // carry k = kc + 32 + 8t + 2j (+1), for A and B alike
-                    const uint32_t af[4] = {u4_get(a[u][0], j), u4_get(a[u][1], j), u4_get(a[u][2], j),
-                                            u4_get(a[u][3], j)};
+                    const uint32_t af[4] = {u4_get(a[h][u][0], j), u4_get(a[h][u][1], j), u4_get(a[h][u][2], j),
+                                            u4_get(a[h][u][3], j)};
                     mma_bf16(c[nt], af, u4_get(xlo, j), u4_get(xhi, j));
                 }
             }
         }
+    };
+    for (int cb = 0; cb < nchunks; cb += GS_UNROLL) {
+        use_half(H0{}, cb);
+        if (cb + GS_UNROLL < nchunks) load_half(H0{}, cb + GS_UNROLL);
+        use_half(H1{}, cb + HALF);
+        if (cb + GS_UNROLL + HALF < nchunks) load_half(H1{}, cb + GS_UNROLL + HALF);
     }
     // c[nt][0..1]: W row r0, batch rows 8nt + 2t, +1; c[nt][2..3]: W row r1.
     float* o = out + (size_t)blockIdx.y * M * N;
