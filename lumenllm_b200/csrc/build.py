@@ -28,7 +28,6 @@ CSRC = Path(__file__).resolve().parent
 MODULES = {
     "core": (["core.cu"], ["common.cuh"]),
     "gemm_f32": (["gemm_f32.cu"], ["common.cuh"]),
-    "gemm_small": (["gemm_small.cu"], ["common.cuh", "mma_utils.cuh"]),
     "gemm_tc": (["gemm_tc.cu"], ["common.cuh", "mma_utils.cuh"]),
     "attn_generic": (["attn_generic.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),

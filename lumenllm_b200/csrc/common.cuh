@@ -46,7 +46,7 @@ __host__ __device__ __forceinline__ int tile_offset(int layout, int r, int e, in
 // kernel before; launched without it, both instructions do nothing. It is on by default
 // (4.11 ms against 4.32 ms a decode step at batch 8 of the 8B shape; the weight-streaming
 // products gain most, 36.6 -> 33.4 us for the gate/up product); LUMEN_PDL=0 turns it off,
-// a comma list of module names (LUMEN_PDL=gemm_tc,gemm_small) turns it on for those alone.
+// a comma list of module names (LUMEN_PDL=gemm_tc,core) turns it on for those alone.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

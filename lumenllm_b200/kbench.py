@@ -1,7 +1,6 @@
 """Micro-benchmarks of single kernels at chosen sizes:
 
     python -m lumenllm_b200.kbench gemm_tc --m 2048 --n 4096 --k 4096 [--silu] [--copies 8] [--reps 5]
-    python -m lumenllm_b200.kbench gemm_small --m 8 --n 4096 --k 4096
     python -m lumenllm_b200.kbench attn_decode --batch 8 --len 1600 --heads 32 --kv-heads 8 --head-dim 128
     python -m lumenllm_b200.kbench attn_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
     python -m lumenllm_b200.kbench add_rmsnorm --m 2048 --n 4096
@@ -57,7 +56,7 @@ def _paged(B, length, nkv, d, dev):
 
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="kbench")
-    ap.add_argument("kernel", choices=["gemm_tc", "gemm_small", "attn_decode", "attn_prefill",
+    ap.add_argument("kernel", choices=["gemm_tc", "attn_decode", "attn_prefill",
                                        "add_rmsnorm", "qk_rope", "argmax", "sample"])
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
@@ -80,13 +79,10 @@ def main(argv=None):
     torch.manual_seed(0)
     bf = torch.bfloat16
     note = ""
-    if a.kernel in ("gemm_tc", "gemm_small"):
+    if a.kernel == "gemm_tc":
         ws = [(torch.randn(a.n, a.k, device=dev) / math.sqrt(a.k)).to(bf) for _ in range(a.copies)]
         x = torch.randn(a.m, a.k, device=dev).to(bf)
-        if a.kernel == "gemm_tc":
-            fns = [lambda w=w: K.gemm_tc(x, w, silu_interleaved=a.silu) for w in ws]
-        else:
-            fns = [lambda w=w: K.gemm_small(x, w) for w in ws]
+        fns = [lambda w=w: K.gemm_tc(x, w, silu_interleaved=a.silu) for w in ws]
         us = _time(fns, a.reps)
         nbytes = a.n * a.k * 2 + a.m * a.k * 2
         flops = 2.0 * a.m * a.n * a.k

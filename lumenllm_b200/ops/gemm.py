@@ -1,12 +1,11 @@
 """bfloat16 matrix products with float32 accumulation.
 
-Two hand-written kernels do the work: the tcgen05 / TMA kernel (csrc/gemm_tc.cu) for every
-shape, in its swapped orientation when there are few rows; and the register-streaming kernel
-(csrc/gemm_small.cu) for up to 16 rows against weights of moderate height, where its k-split
-over many small blocks and its fused SiLU prologue win. A product may come back as S partial
-sums [S, M, N] for the consumer to add. The library product (cuBLAS through torch, as the
-reference uses cuBLASLt: crates/aegisllm-cuda/src/cuda/runtime/cublaslt.rs:57-165) stands only
-where a row of the operands is not a multiple of 16 bytes, which the TMA cannot address.
+The tcgen05 / TMA kernels (csrc/gemm_tc.cu) do the work for every shape: two SMs a tile for
+prompts, a weight-streaming orientation with k split for decode and short prompts. A product
+may come back as S partial sums [S, M, N] for the consumer to add, or be added to the residual
+stream in place. The library product (cuBLAS through torch, as the reference uses cuBLASLt:
+crates/aegisllm-cuda/src/cuda/runtime/cublaslt.rs:57-165) stands only where a row of the
+operands is not a multiple of 16 bytes, which the TMA cannot address.
 """
 from __future__ import annotations
 
@@ -18,13 +17,6 @@ from .native import KernelError
 torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
 torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
-
-SMALL_MAX_N = 8192      # tallest and widest weight the register-streaming kernel is preferred for
-SMALL_MAX_K = 8192
-
-
-def takes_small(M: int, Kdim: int, N: int) -> bool:
-    return M <= K.SMALL_M and Kdim % 8 == 0 and N <= SMALL_MAX_N and Kdim <= SMALL_MAX_K
 
 
 def takes_tc(x: torch.Tensor, w: torch.Tensor) -> bool:
@@ -42,9 +34,7 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, split_ok: bool = False, add_to=N
         raise KernelError("gemm_bf16: no CPU path exists")
     if not x.is_contiguous():
         x = x.contiguous()
-    if takes_small(x.shape[0], x.shape[1], w.shape[0]):
-        part = K.gemm_small(x, w)
-    elif takes_tc(x, w):
+    if takes_tc(x, w):
         if (add_to is not None and add_to.is_contiguous() and add_to.data_ptr() % 16 == 0
                 and K.gemm_tc_adds(x.shape[0], w.shape[0])):
             return K.gemm_tc(x, w, add_to=add_to)
@@ -63,13 +53,3 @@ def gemm_gate_up_silu(x: torch.Tensor, w_interleaved: torch.Tensor):
         return K.gemm_tc(x if x.is_contiguous() else x.contiguous(), w_interleaved,
                          silu_interleaved=True)
     return None
-
-
-def gemm_down_silu(gu: torch.Tensor, w: torch.Tensor, interleaved: bool):
-    """(silu(gate) * up) @ w.T for gu float32 [M, 2K] (or [S, M, 2K] partials), M <= 16, with
-    the activation applied while the rows are staged. Returns [S2, M, N] partials, or None if
-    this shape is not taken (the caller then runs the two steps apart)."""
-    M = gu.shape[-2]
-    if w.dtype != torch.bfloat16 or not takes_small(M, w.shape[1], w.shape[0]):
-        return None
-    return K.gemm_small(gu, w, silu_gate_up=True, interleaved=interleaved)

@@ -182,39 +182,6 @@ def gemm_f32(a, w, out=None):
     return out
 
 
-SMALL_M = 16   # the weight-streaming product takes up to this many rows
-
-
-def gemm_small_splits(N, K) -> int:
-    return int(int_fn("gemm_small", "lumen_gemm_small_splits", [c_int, c_int])(int(N), int(K)))
-
-
-def gemm_small(x, w, silu_gate_up=False, interleaved=False):
-    """Weight-streaming product for M <= 16 rows: float32 partials [S, M, N] of x @ w.T.
-    x bfloat16 [M, K]; or, with silu_gate_up, float32 [M, 2K] holding gate | up (interleaved:
-    gate_i, up_i in columns 2i, 2i+1), of which silu(gate) * up is multiplied.
-    w bfloat16 [N, K], K a multiple of 8."""
-    require(w, BF16, "gemm_small.w")
-    N, K = w.shape
-    xs = 1
-    if silu_gate_up:
-        x, xs = _partials(x, "gemm_small.x")
-        if x.shape[2] != 2 * K:
-            raise KernelError(f"gemm_small: gate|up input must be [M, {2 * K}] or [S, M, {2 * K}]")
-        M = x.shape[1]
-    else:
-        require(x, BF16, "gemm_small.x")
-        if x.dim() != 2 or x.shape[1] != K:
-            raise KernelError(f"gemm_small: inner sizes differ ({x.shape[1]} vs {K})")
-        M = x.shape[0]
-    S = gemm_small_splits(N, K)
-    out = torch.empty((S, M, N), dtype=F32, device=x.device)
-    f = fn("gemm_small", "lumen_gemm_small", [P, c_int, c_int, P, P, c_int, c_int, c_int, P])
-    mode = 0 if not silu_gate_up else (2 if interleaved else 1)
-    check(f(ptr(x), mode, xs, ptr(w), ptr(out), M, N, K, stream_ptr()), "gemm_small")
-    return out
-
-
 def gemm_tc_splits(M, N, K, silu=False) -> int:
     return int(int_fn("gemm_tc", "lumen_gemm_tc_splits", [c_int, c_int, c_int, c_int])(
         int(M), int(N), int(K), 1 if silu else 0))

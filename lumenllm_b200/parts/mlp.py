@@ -6,7 +6,7 @@ Gate and up weights are stacked so that both cost one product. For bfloat16 thei
 are interleaved (gate_0, up_0, gate_1, up_1, ...): then a tile of the product holds both
 halves of each pair, and the tensor-core kernel applies SiLU(gate) * up in its epilogue
 and writes bfloat16 directly. With few rows the product returns float32 (partial sums)
-and the activation is applied while the down projection stages its input.
+and a small kernel adds them and applies the activation.
 """
 from __future__ import annotations
 
@@ -51,9 +51,5 @@ class SwiGLU:
             if z is not None:
                 return self.down(z, split_ok=True, add_to=residual)
         gu = self.gate_up(y, split_ok=True)        # float32 [N, 2I], possibly S partials
-        if not self.down.f32:
-            out = G.gemm_down_silu(gu, self.down.weight, self.interleaved)   # few rows
-            if out is not None:
-                return out
         z = K.silu_mul(gu, self.runtime.dtype, interleaved=self.interleaved)
         return self.down(z, split_ok=True)

@@ -339,39 +339,6 @@ def test_gemm_f32_is_true_float32(wdtype, M, N, K_):
     assert torch.equal(one[0], out[M // 2])
 
 
-@pytest.mark.parametrize("M,N,K_", [(1, 4096, 4096), (8, 6144, 4096), (3, 311, 80), (16, 130, 1000),
-                                    (9, 24576, 512), (5, 96, 12288), (2, 16, 8)])
-def test_gemm_small_streams_weights(M, N, K_):
-    """The few-row product: against float64 of the same bfloat16 inputs; a row's result does
-    not depend on the batch; the k splits depend on the weight's shape only."""
-    from lumenllm_b200.ops import kernels as K
-    g = gen(14)
-    x = torch.randn(M, K_, generator=g).to(BF16)
-    w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(BF16)
-    part = K.gemm_small(dev(x), dev(w)).cpu()
-    assert part.shape == (K.gemm_small_splits(N, K_), M, N)
-    out = part.sum(0)
-    ref = x.double() @ w.double().T
-    assert float((out.double() - ref).abs().max()) < 1e-4
-    one = K.gemm_small(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w)).cpu()
-    assert torch.equal(one[:, 0], part[:, M // 2])
-
-
-@pytest.mark.parametrize("M,I,H", [(4, 12288, 256), (16, 176, 80), (1, 512, 96)])
-def test_gemm_small_with_silu_prologue(M, I, H):
-    from lumenllm_b200.ops import kernels as K
-    g = gen(15)
-    gu = torch.randn(M, 2 * I, generator=g)
-    w = (torch.randn(H, I, generator=g) / math.sqrt(I)).to(BF16)
-    z = P.swiglu(gu[:, :I], gu[:, I:]).to(BF16)
-    ref = z.double() @ w.double().T
-    out = K.gemm_small(dev(gu), dev(w), silu_gate_up=True).cpu().sum(0)
-    assert float((out.double() - ref).abs().max()) < 2e-3 * max(1.0, float(ref.abs().max()))
-    halves = torch.stack([0.5 * gu, 0.5 * gu])
-    out2 = K.gemm_small(dev(halves), dev(w), silu_gate_up=True).cpu().sum(0)
-    assert torch.equal(out, out2)
-
-
 @pytest.mark.parametrize("M,N,K_", [(128, 256, 64), (200, 300, 320), (2048, 1024, 4096), (1, 256, 64),
                                     (8, 4096, 4096), (19, 311, 80), (33, 1000, 1000), (64, 6144, 1024),
                                     (65, 130, 72), (130, 17, 1000), (16, 151936 // 4 + 8, 256)])
@@ -435,15 +402,10 @@ def test_gemm_tc_with_silu_epilogue_on_interleaved_rows(M, I, H):
     ref = P.swiglu(x.float() @ wg.float().T, x.float() @ wu.float().T)
     assert z.shape == (M, I)
     assert float(((z - ref).abs() / (1 + ref.abs())).max()) < 2 ** -7
-    # the same through the float32 product, the activation kernel and the down prologue
+    # the same through the float32 product and the activation kernel
     gu = K.gemm_tc(dev(x), dev(w))
     z2 = K.silu_mul(gu, BF16, interleaved=True).cpu().float()
     assert float(((z2 - ref).abs() / (1 + ref.abs())).max()) < 2 ** -7
-    if M <= 16:
-        wd = (torch.randn(H, I, generator=g) / math.sqrt(I)).to(BF16)
-        out = K.gemm_small(gu, dev(wd), silu_gate_up=True, interleaved=True).cpu().sum(0)
-        ref2 = ref.to(BF16).double() @ wd.double().T
-        assert float((out.double() - ref2).abs().max()) < 2e-2 * max(1.0, float(ref2.abs().max()))
 
 
 def test_argmax_ties_and_odd_vocab():
@@ -574,8 +536,8 @@ def test_sampler_with_drawn_settings(V, rows):
 
 
 def test_products_of_drawn_shapes_through_the_router():
-    """Shapes drawn from a fixed seed across every regime of the product's routing (streaming
-    few-row kernel, weight-streaming tcgen05 orientation with k split, single-SM tiles with
+    """Shapes drawn from a fixed seed across every regime of the product's routing
+    (weight-streaming tcgen05 orientation with k split, single-SM tiles with
     narrow widths or k split, two SMs a tile with staged stores, the library where a row is
     no multiple of 16 bytes): all against the double-precision product."""
     import random
