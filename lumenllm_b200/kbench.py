@@ -3,7 +3,7 @@
     python -m lumenllm_b200.kbench gemm_tc --m 2048 --n 4096 --k 4096 [--silu] [--copies 8] [--reps 5]
     python -m lumenllm_b200.kbench attn_decode --batch 8 --len 1600 --heads 32 --kv-heads 8 --head-dim 128
     python -m lumenllm_b200.kbench attn_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
-    python -m lumenllm_b200.kbench add_rmsnorm --m 2048 --n 4096
+    python -m lumenllm_b200.kbench add_rmsnorm --m 2048 --n 4096 [--splits 9]
     python -m lumenllm_b200.kbench qk_rope --m 2048 --heads 32 --kv-heads 8 --head-dim 128
     python -m lumenllm_b200.kbench argmax --m 8 --n 151936
     python -m lumenllm_b200.kbench sample --m 8 --n 151936 [--top-k 50] [--top-p 0.9]
@@ -58,6 +58,7 @@ def main(argv=None):
     ap = argparse.ArgumentParser(prog="kbench")
     ap.add_argument("kernel", choices=["gemm_tc", "attn_decode", "attn_prefill",
                                        "add_rmsnorm", "qk_rope", "argmax", "sample"])
+    ap.add_argument("--splits", type=int, default=1, help="add_rmsnorm: partial sums to add")
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
     ap.add_argument("--min-p", type=float, default=0.0)
@@ -107,11 +108,11 @@ def main(argv=None):
         note = f"{flops / us / 1e6:.1f} TFLOP/s"
     elif a.kernel == "add_rmsnorm":
         hs = [torch.randn(a.m, a.n, device=dev) for _ in range(a.copies)]
-        ds = [torch.randn(1, a.m, a.n, device=dev) for _ in range(a.copies)]
+        ds = [torch.randn(a.splits, a.m, a.n, device=dev) for _ in range(a.copies)]
         w = torch.ones(a.n, device=dev)
         fns = [lambda h=h, d=d: K.add_rmsnorm(h, d, w, 1e-6, bf) for h, d in zip(hs, ds)]
         us = _time(fns, a.reps)
-        note = f"{a.m * a.n * 14 / us / 1e3:.0f} GB/s"
+        note = f"{a.m * a.n * (10 + 4 * a.splits) / us / 1e3:.0f} GB/s"
     elif a.kernel in ("argmax", "sample"):
         lgs = [torch.randn(a.m, a.n, device=dev) * 3 for _ in range(a.copies)]
         if a.kernel == "argmax":
