@@ -290,10 +290,10 @@ DECODE_MAX_SEGS = 32
 
 def decode_segment_pages(B, nkv) -> int:
     """Pages a decode-attention block walks (unless the sequence is longer than 32 segments):
-    8 when the batch brings blocks enough, fewer for a small batch, so that a short batch is
-    spread over more SMs. A function of the batch and the kv heads only, never of the page
+    8 when the batch brings blocks enough, fewer (down to 2) for a small batch, so that a short
+    batch is spread over more SMs. A function of the batch and the kv heads only, never of the page
     table's width, so a wider (padded) table does not change a result."""
-    return max(1, min(8, (B * nkv) // 8))
+    return max(2, min(8, (B * nkv) // 8))
 
 
 def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
