@@ -237,11 +237,13 @@ def main() -> int:
     e2e_runs = sorted((e2e_run(built, B, min(steps, 64), seed=2) for _ in range(3)), key=lambda r: r["tok_s"])
     e2e = e2e_runs[1]
     e2e["window"] = (min(r["window"][0] for r in e2e_runs), max(r["window"][1] for r in e2e_runs))
-    points, windows = {}, [main_run["window"], e2e["window"]] + pre_windows
+    points, points_frac, windows = {}, {}, [main_run["window"], e2e["window"]] + pre_windows
     if not args.no_points:
         for b in (1, 64):
             r = decode_run(eng, b, min(steps, 32), warmup, seed=10 + b)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
+            got = (weight_bytes + b * r["mean_len"] * nums["kv_bytes_per_token"]) / (r["ms"] * 1e-3) / 1e9
+            points_frac[f"decode_b{b}"] = round(got / pk["hbm_gbs"], 4)
             windows.append(r["window"])
     time.sleep(0.3)
     clocks.stop()
@@ -269,6 +271,7 @@ def main() -> int:
         "roofline": {"bound": "hbm", "achieved": round(achieved, 1), "peak": pk["hbm_gbs"],
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
+        "points_roofline_frac": points_frac,     # the same bytes-over-time figure as "roofline"
     }
     print(json.dumps(out))
     return 0

@@ -136,12 +136,83 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S
     }
 }
 
+// The same for many rows (prompts) of at most 16 x 512 values: a thread keeps its four groups
+// of four values in registers, so all loads of a row are in flight at once and nothing goes
+// through shared memory. The norm's weight is loaded before the kernel ahead has finished.
+#define ARN_GROUPS 4
+template <typename TOut>
+__global__ void __launch_bounds__(512)
+add_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
+                        const float* __restrict__ w, float eps, TOut* __restrict__ y,
+                        const int* __restrict__ rows, int H, int write_h) {
+    __shared__ float red[32];
+    const int b = blockIdx.x;
+    float4 g[ARN_GROUPS], x[ARN_GROUPS];
+#pragma unroll
+    for (int j = 0; j < ARN_GROUPS; ++j) {
+        const int i = (j * blockDim.x + threadIdx.x) * 4;
+        g[j] = i < H ? load4(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    pdl_wait();      // nothing else of this kernel touches global memory before this
+    pdl_trigger();
+    const int r = rows ? rows[b] : b;
+    float* hr = h + (size_t)r * H;
+    const float* dr = delta + (size_t)r * H;
+#pragma unroll
+    for (int j = 0; j < ARN_GROUPS; ++j) {
+        const int i = (j * blockDim.x + threadIdx.x) * 4;
+        x[j] = i < H ? load4(hr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    for (int s = 0; s < S; ++s) {             // the partial sums are added in rising order
+        float4 d[ARN_GROUPS];
+#pragma unroll
+        for (int j = 0; j < ARN_GROUPS; ++j) {
+            const int i = (j * blockDim.x + threadIdx.x) * 4;
+            d[j] = i < H ? load4(dr + (size_t)s * delta_stride + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < ARN_GROUPS; ++j) { x[j].x += d[j].x; x[j].y += d[j].y; x[j].z += d[j].z; x[j].w += d[j].w; }
+    }
+    float ss = 0.0f;
+#pragma unroll
+    for (int j = 0; j < ARN_GROUPS; ++j) {
+        const int i = (j * blockDim.x + threadIdx.x) * 4;
+        if (write_h && S > 0 && i < H) *reinterpret_cast<float4*>(hr + i) = x[j];
+        ss += x[j].x * x[j].x;
+        ss += x[j].y * x[j].y;
+        ss += x[j].z * x[j].z;
+        ss += x[j].w * x[j].w;
+    }
+    ss = block_sum(ss, red);
+    const float scale = 1.0f / sqrtf(ss / (float)H + eps);
+    TOut* yr = y + (size_t)b * H;
+#pragma unroll
+    for (int j = 0; j < ARN_GROUPS; ++j) {
+        const int i = (j * blockDim.x + threadIdx.x) * 4;
+        if (i < H)
+            Pack4<TOut>::store(yr + i, x[j].x * scale * g[j].x, x[j].y * scale * g[j].y, x[j].z * scale * g[j].z,
+                               x[j].w * scale * g[j].w);
+    }
+}
+
 LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long long delta_stride,
                                 const float* w, float eps, void* y, int y_is_bf16,
                                 const int* rows, int n_rows, int H, int write_h,
                                 cudaStream_t stream) {
     if (n_rows <= 0) return 0;
     if (H <= 0 || n_delta < 0) return LUMEN_ERR_BAD_ARGUMENT;
+    if (n_rows >= 2 * 148 && (H & 3) == 0 && H <= 512 * 4 * ARN_GROUPS) {
+        int t = ((H / (4 * ARN_GROUPS) + 31) / 32) * 32;
+        if (t < 64) t = 64;
+        if (y_is_bf16)
+            lumen_launch(add_rmsnorm_rows_kernel<__nv_bfloat16>, dim3(n_rows), dim3(t), 0, stream, h, delta, n_delta,
+                         (size_t)delta_stride, w, eps, (__nv_bfloat16*)y, rows, H, write_h);
+        else
+            lumen_launch(add_rmsnorm_rows_kernel<float>, dim3(n_rows), dim3(t), 0, stream, h, delta, n_delta,
+                         (size_t)delta_stride, w, eps, (float*)y, rows, H, write_h);
+        LUMEN_LAUNCH_CHECK();
+        return 0;
+    }
     const size_t smem = (size_t)H * sizeof(float);
     if (smem > 200 * 1024) return LUMEN_ERR_UNSUPPORTED;
     // Few rows (decode): one row per block cannot fill the GPU, so each block is made wide and
@@ -428,6 +499,112 @@ qk_norm_rope_store_d128_kernel(const float* __restrict__ qkv, int S, size_t spli
     }
 }
 
+// The same for many tokens (prompts), laid out so that the rotation needs no exchange between
+// lanes: a warp takes QKR_HPW consecutive heads of its token two at a time, the lower 16 lanes
+// one head and the upper 16 the next; a lane holds values 4l..4l+3 and their partners
+// 64+4l..64+4l+3, and a head's sum of squares runs over 16 lanes. The rotation table and the
+// token's page are looked up once a warp, the norms' weights before the kernel ahead has
+// finished. Which of q, k or v a lane's head is decides by selects, not branches.
+#define QKR_HPW 4
+template <typename T>
+__global__ void __launch_bounds__(128, 8)
+qk_norm_rope_store_d128_rows_kernel(const float* __restrict__ qkv, int S, size_t split_stride,
+                                    const float* __restrict__ qw, const float* __restrict__ kw, float eps,
+                                    const float2* __restrict__ cs, int rot, const int* __restrict__ cache_pos,
+                                    const int* __restrict__ tok_seq, const int* __restrict__ block_table,
+                                    int bt_stride, T* __restrict__ q_out, T* __restrict__ kcache,
+                                    T* __restrict__ vcache, int nq, int nkv, int layout) {
+    constexpr int d = 128;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int li = lane & 15, up = lane >> 4;
+    const int n = blockIdx.x;
+    const int head0 = (blockIdx.y * 4 + warp) * QKR_HPW;
+    const int nheads = nq + 2 * nkv;
+    const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
+    const float4 gq_lo = qw ? load4(qw + 4 * li) : one, gq_hi = qw ? load4(qw + 64 + 4 * li) : one;
+    const float4 gk_lo = kw ? load4(kw + 4 * li) : one, gk_hi = kw ? load4(kw + 64 + 4 * li) : one;
+    pdl_wait();      // nothing else of this kernel touches global memory before this
+    pdl_trigger();
+    if (head0 >= nheads) return;
+    float4 lo[QKR_HPW / 2], hi[QKR_HPW / 2];
+    const float* src = qkv + ((size_t)n * nheads + head0 + up) * d + 4 * li;
+#pragma unroll
+    for (int j = 0; j < QKR_HPW / 2; ++j) {
+        const bool have = head0 + 2 * j + up < nheads;
+        lo[j] = have ? load4(src + 2 * j * d) : make_float4(0.f, 0.f, 0.f, 0.f);
+        hi[j] = have ? load4(src + 2 * j * d + 64) : make_float4(0.f, 0.f, 0.f, 0.f);
+    }
+    float4 c01 = make_float4(1.f, 0.f, 1.f, 0.f), c23 = c01;
+    if (rot == d) {
+        const float4* csn = reinterpret_cast<const float4*>(cs + (size_t)n * 64 + 4 * li);
+        c01 = csn[0];        // (cos, sin) of 4 consecutive pairs
+        c23 = csn[1];
+    }
+    const int cp = cache_pos[n];
+    const int page = head0 + QKR_HPW > nq ? block_table[(size_t)tok_seq[n] * bt_stride + cp / LUMEN_PAGE] : 0;
+    const int off_lo = tile_offset(layout, cp % LUMEN_PAGE, 4 * li, d);
+    const int off_hi = tile_offset(layout, cp % LUMEN_PAGE, 64 + 4 * li, d);
+    for (int s = 1; s < S; ++s) {             // the partial sums are added in rising order
+        float4 lo2[QKR_HPW / 2], hi2[QKR_HPW / 2];
+#pragma unroll
+        for (int j = 0; j < QKR_HPW / 2; ++j) {
+            const bool have = head0 + 2 * j + up < nheads;
+            lo2[j] = have ? load4(src + 2 * j * d + (size_t)s * split_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+            hi2[j] = have ? load4(src + 2 * j * d + 64 + (size_t)s * split_stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+        }
+#pragma unroll
+        for (int j = 0; j < QKR_HPW / 2; ++j) {
+            lo[j].x += lo2[j].x; lo[j].y += lo2[j].y; lo[j].z += lo2[j].z; lo[j].w += lo2[j].w;
+            hi[j].x += hi2[j].x; hi[j].y += hi2[j].y; hi[j].z += hi2[j].z; hi[j].w += hi2[j].w;
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < QKR_HPW / 2; ++j) {
+        const int head = head0 + 2 * j + up;
+        const bool is_q = head < nq;
+        const bool is_k = !is_q && head < nq + nkv;
+        float4 a = lo[j], b = hi[j];
+        float ss = a.x * a.x;
+        ss += a.y * a.y;
+        ss += a.z * a.z;
+        ss += a.w * a.w;
+        ss += b.x * b.x;
+        ss += b.y * b.y;
+        ss += b.z * b.z;
+        ss += b.w * b.w;
+#pragma unroll
+        for (int m = 8; m >= 1; m >>= 1) ss += __shfl_xor_sync(0xffffffffu, ss, m);   // over the head's 16 lanes
+        if ((is_q && qw) || (is_k && kw)) {
+            const float scale = 1.0f / sqrtf(ss / (float)d + eps);
+            const float4 g_lo = is_q ? gq_lo : gk_lo, g_hi = is_q ? gq_hi : gk_hi;
+            a.x = a.x * scale * g_lo.x; a.y = a.y * scale * g_lo.y; a.z = a.z * scale * g_lo.z; a.w = a.w * scale * g_lo.w;
+            b.x = b.x * scale * g_hi.x; b.y = b.y * scale * g_hi.y; b.z = b.z * scale * g_hi.z; b.w = b.w * scale * g_hi.w;
+        }
+        if (is_q || is_k) {      // x'_i = x_i cos - x_{i+64} sin, x'_{i+64} = x_i sin + x_{i+64} cos
+            const float4 a0 = a;
+            a.x = a0.x * c01.x - b.x * c01.y; a.y = a0.y * c01.z - b.y * c01.w;
+            a.z = a0.z * c23.x - b.z * c23.y; a.w = a0.w * c23.z - b.w * c23.w;
+            b.x = a0.x * c01.y + b.x * c01.x; b.y = a0.y * c01.w + b.y * c01.z;
+            b.z = a0.z * c23.y + b.z * c23.x; b.w = a0.w * c23.w + b.w * c23.z;
+        }
+        if (head < nheads) {
+            T* p_lo;
+            T* p_hi;
+            if (is_q) {
+                p_lo = q_out + ((size_t)n * nq + head) * d + 4 * li;
+                p_hi = p_lo + 64;
+            } else {
+                const int kvh = is_k ? head - nq : head - nq - nkv;
+                T* tile = (is_k ? kcache : vcache) + ((size_t)page * nkv + kvh) * LUMEN_PAGE * d;
+                p_lo = tile + off_lo;
+                p_hi = tile + off_hi;
+            }
+            Pack4<T>::store(p_lo, a.x, a.y, a.z, a.w);
+            Pack4<T>::store(p_hi, b.x, b.y, b.z, b.w);
+        }
+    }
+}
+
 LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, int n_splits, const float* qw, const float* kw,
                                        float eps, const float* cs, int rot, const int* cache_pos,
                                        const int* tok_seq, const int* block_table, int bt_stride,
@@ -443,6 +620,21 @@ LUMEN_API int lumen_qk_norm_rope_store(const float* qkv, int n_splits, const flo
     const int nheads = nq + 2 * nkv;
     if (nheads == 0) return 0;
     if ((nheads + warps - 1) / warps > 65535) return LUMEN_ERR_UNSUPPORTED;
+    if (d == 128 && (rot == 128 || rot == 0) && N >= 2 * 148) {
+        dim3 g(N, (nheads + 4 * QKR_HPW - 1) / (4 * QKR_HPW));
+        const size_t st = (size_t)N * nheads * d;
+        if (is_bf16)
+            lumen_launch(qk_norm_rope_store_d128_rows_kernel<__nv_bfloat16>, dim3(g), dim3(128), 0, stream,
+                qkv, n_splits, st, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
+                bt_stride, (__nv_bfloat16*)q_out, (__nv_bfloat16*)kcache, (__nv_bfloat16*)vcache, nq, nkv,
+                layout);
+        else
+            lumen_launch(qk_norm_rope_store_d128_rows_kernel<float>, dim3(g), dim3(128), 0, stream,
+                qkv, n_splits, st, qw, kw, eps, (const float2*)cs, rot, cache_pos, tok_seq, block_table,
+                bt_stride, (float*)q_out, (float*)kcache, (float*)vcache, nq, nkv, layout);
+        LUMEN_LAUNCH_CHECK();
+        return 0;
+    }
     if (d == 128 && (rot == 128 || rot == 0)) {
         dim3 g8(N, (nheads + 7) / 8);
         const size_t st = (size_t)N * nheads * d;

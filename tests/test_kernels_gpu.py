@@ -33,10 +33,11 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("out_dtype", [F32, BF16])
-@pytest.mark.parametrize("H,S", [(1000, 0), (80, 1), (4096 + 48, 3)])
-def test_add_rmsnorm(out_dtype, H, S):
+@pytest.mark.parametrize("N", [13, 301])      # few rows and many: kernels of their own
+@pytest.mark.parametrize("H,S", [(1000, 0), (80, 1), (4096 + 48, 3), (8192 + 8, 2)])
+def test_add_rmsnorm(out_dtype, H, S, N):
     from lumenllm_b200.ops import kernels as K
-    N, eps = 13, 1e-5
+    eps = 1e-5
     g = gen(1)
     h = torch.randn(N, H, generator=g)
     w = 1 + 0.1 * torch.randn(H, generator=g)
@@ -90,12 +91,13 @@ def to_sw128(x):
 
 
 @pytest.mark.parametrize("dtype", [F32, BF16])
-@pytest.mark.parametrize("nq,nkv,d,rot", [(6, 3, 48, 48), (5, 5, 16, 8), (8, 2, 128, 128), (3, 1, 80, 80)])
-def test_qk_norm_rope_store(dtype, nq, nkv, d, rot):
+@pytest.mark.parametrize("nq,nkv,d,rot", [(6, 3, 48, 48), (5, 5, 16, 8), (8, 2, 128, 128), (3, 1, 80, 80),
+                                          (7, 3, 128, 128), (4, 4, 128, 128)])
+@pytest.mark.parametrize("lens", [[70, 3], [250, 75]])   # few tokens and many: kernels of their own
+def test_qk_norm_rope_store(dtype, nq, nkv, d, rot, lens):
     from lumenllm_b200.ops import kernels as K
     g = gen(3)
-    lens = [70, 3]                         # two sequences; the first starts at position 60
-    starts = [60, 0]
+    starts = [60, 0]                       # two sequences; the first starts at position 60
     N = sum(lens)
     qkv = torch.randn(N, (nq + 2 * nkv) * d, generator=g)
     qw = 1 + 0.1 * torch.randn(d, generator=g)
@@ -105,7 +107,7 @@ def test_qk_norm_rope_store(dtype, nq, nkv, d, rot):
     pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(I32)
     seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).to(I32)
     n_pages = 12
-    table = torch.tensor([[9, 4, 7], [2, 0, 0]], dtype=I32)
+    table = torch.tensor([[9, 4, 7, 1, 10], [2, 6, 0, 0, 0]], dtype=I32)
     kc = torch.zeros(n_pages, nkv, 64, d, dtype=dtype)
     vc = torch.zeros_like(kc)
     kcd, vcd = dev(kc), dev(vc)
