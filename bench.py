@@ -165,7 +165,6 @@ def e2e_run(built, B, steps, seed):
     lens = torch.randint(PROMPT_LO, PROMPT_HI + 1, (B,), generator=g).tolist()
     prompts = [torch.randint(0, built.engine.vocab_size, (n,), generator=g).tolist() for n in lens]
     reqs = [GenerateRequest(p, steps + 1) for p in prompts]
-    built.generate(reqs[:1], eos_token_ids=[]) if False else None
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = built.generate(reqs, eos_token_ids=[], max_batch=B)
