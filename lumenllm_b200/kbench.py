@@ -112,7 +112,8 @@ def main(argv=None):
         w = torch.ones(a.n, device=dev)
         fns = [lambda h=h, d=d: K.add_rmsnorm(h, d, w, 1e-6, bf) for h, d in zip(hs, ds)]
         us = _time(fns, a.reps)
-        note = f"{a.m * a.n * (10 + 4 * a.splits) / us / 1e3:.0f} GB/s"
+        # h read, y written; with partial sums those are read and h is written back
+        note = f"{a.m * a.n * ((10 + 4 * a.splits) if a.splits else 6) / us / 1e3:.0f} GB/s"
     elif a.kernel in ("argmax", "sample"):
         lgs = [torch.randn(a.m, a.n, device=dev) * 3 for _ in range(a.copies)]
         if a.kernel == "argmax":
