@@ -181,6 +181,35 @@ def test_want_selects_rows_and_may_be_empty(dtype, plain, engines):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", ["B", "C"])
+def test_two_live_batches_take_turns(name, dtype, plain, engines):
+    """Two batches hold the cache at the same time and are stepped in turn (prompts of the
+    first, prompts of the second, then a token each, alternately): neither reads the other's
+    keys, and the captured decode step serves whichever slots a step names."""
+    from lumenllm_b200 import StepEntry
+    cfg, w = plain[name]
+    eng = engines(name, dtype)
+    seqs = seeded_tokens(cfg["vocab_size"], [70, 9, 131, 40, 66], 61)
+    refs = [P.forward_logits(cfg, w, s) for s in seqs]
+    groups = ([0, 1], [2, 3, 4])
+    cuts = [len(s) - 6 for s in seqs]
+    slots = [eng.alloc_slot() for _ in seqs]
+    for grp in groups:
+        lg = eng.step([StepEntry(slots[i], seqs[i][:cuts[i]], [cuts[i] - 1]) for i in grp]).cpu()
+        for k, i in enumerate(grp):
+            check(lg[k:k + 1], refs[i][cuts[i] - 1:cuts[i]], dtype, f"{name} prompts of {grp}, request {i}")
+    for t in range(6):
+        for grp in groups:
+            lg = eng.step([StepEntry(slots[i], [seqs[i][cuts[i] + t]], [0]) for i in grp]).cpu()
+            for k, i in enumerate(grp):
+                check(lg[k:k + 1], refs[i][cuts[i] + t:cuts[i] + t + 1], dtype,
+                      f"{name} turn {t} of {grp}, request {i}")
+    for s in slots:
+        eng.free_slot(s)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
 def test_padding_changes_nothing(dtype, plain, engines):
     from lumenllm_b200 import StepEntry
     cfg, w = plain["A"]
