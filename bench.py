@@ -233,7 +233,7 @@ def main() -> int:
     pre_frac = flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
 
     # three runs, the median: a run is a quarter of a second, and host jitter shows in it
-    e2e_runs = sorted((e2e_run(built, B, min(steps, 64), seed=2) for _ in range(3)), key=lambda r: r["tok_s"])
+    e2e_runs = sorted((e2e_run(built, B, steps, seed=2) for _ in range(3)), key=lambda r: r["tok_s"])
     e2e = e2e_runs[1]
     e2e["window"] = (min(r["window"][0] for r in e2e_runs), max(r["window"][1] for r in e2e_runs))
     points, points_frac, windows = {}, {}, [main_run["window"], e2e["window"]] + pre_windows
