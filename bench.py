@@ -185,7 +185,17 @@ def main() -> int:
                     help="fewer layers than the shape has, for small memory (named in config)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--context", type=int, default=CONTEXT,
+                    help="context length (default: the baseline configuration's)")
+    ap.add_argument("--prompt-len", default=f"{PROMPT_LO}:{PROMPT_HI}", metavar="LO:HI",
+                    help="prompt lengths are drawn uniformly from this range")
     args = ap.parse_args()
+    globals()["CONTEXT"] = args.context
+    lo, _, hi = args.prompt_len.partition(":")
+    globals()["PROMPT_LO"], globals()["PROMPT_HI"] = int(lo), int(hi or lo)
+    if not 1 <= PROMPT_LO <= PROMPT_HI or PROMPT_HI + 64 + max(3, args.warmup) + max(1, args.steps) + 64 > CONTEXT:
+        print("bench.py: prompts, warm-up and steps must fit the context", file=sys.stderr)
+        return 2
     if args.impl == "reference":
         print(json.dumps({"impl": "reference", "unavailable":
                           "the reference is Rust + NVRTC CUDA for SM120; no Rust toolchain on "
@@ -206,11 +216,16 @@ def main() -> int:
     B = args.batch
     top_b = B if args.no_points else max(B, 64)
     max_tokens = max(B * CONTEXT, top_b * (PROMPT_HI + 64 + warmup + steps + 64))
+    nums = model_numbers(cfg, args.layers)
+    need = max_tokens * nums["kv_bytes_per_token"] + 2 * (nums["layer_params"] + nums["head_params"])
+    if need > 165e9:
+        print(f"bench.py: {need / 1e9:.0f} GB of weights and cache do not fit; use --no-points, a "
+              "smaller --batch or --context, or fewer --layers", file=sys.stderr)
+        return 2
     eng = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=max_tokens,
                              max_slots=max(top_b, 8), context_size=CONTEXT)
     eng.graphs.min_width = CONTEXT // 64
     built = BuiltEngine(eng, SamplingDefaults(), B)
-    nums = model_numbers(cfg, args.layers)
     clocks = Clocks()
     clocks.start()
 
