@@ -6,6 +6,7 @@
 //
 // Inputs that come from a split matrix product arrive as S partial results [S, rows, width];
 // they are added in rising order of S while they are read.
+#include <cooperative_groups.h>
 #include "common.cuh"
 
 template <typename T> struct Pack4;
@@ -136,6 +137,85 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S
     }
 }
 
+// The same for a single row (decode at batch 1), spread over a cluster of blocks. In a decode step the
+// norm stands between two weight-streaming products whose blocks fill every SM with 181 KB of
+// shared memory and some 46 K registers; a block of 1,024 threads finds no room beside them
+// and starts only when one of them has left, while blocks of 256 threads fit, sit waiting at
+// the dependency before the product ahead has finished, and have their weights loaded by
+// then. So a row is taken by ARN_CLUSTER-or-fewer blocks of at most 256 threads, one group of
+// four values a thread; each block sums its squares, writes that sum into every block's shared
+// memory, and after ONE cluster barrier every block adds the sums in rank order (the same
+// total in all of them). Blocks only write to their peers before the barrier and read their
+// own memory after it, so a block may leave as soon as it is done.
+#define ARN_CLUSTER 8
+template <typename TOut>
+__global__ void __launch_bounds__(256, 4)
+add_rmsnorm_cluster_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
+                           const float* __restrict__ w, float eps, TOut* __restrict__ y,
+                           const int* __restrict__ rows, int H, int write_h) {
+    namespace cg = cooperative_groups;
+    __shared__ float red[32];
+    __shared__ float sums[ARN_CLUSTER];
+    cg::cluster_group cluster = cg::this_cluster();
+    const int rank = (int)cluster.block_rank(), nb = (int)cluster.num_blocks();
+    const int b = blockIdx.x / nb;
+    const int i = (rank * (int)blockDim.x + (int)threadIdx.x) * 4;
+    const bool mine = i < H;
+    const float4 g = mine ? load4(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    pdl_wait();      // nothing else of this kernel touches global memory before this
+    pdl_trigger();
+    const int r = rows ? rows[b] : b;
+    float* hr = h + (size_t)r * H;
+    const float* dr = delta + (size_t)r * H;
+    float4 x = mine ? load4(hr + i) : make_float4(0.f, 0.f, 0.f, 0.f);
+    // the partial sums are added in rising order; their loads go out eight at a time
+    for (int s0 = 0; s0 < S && mine; s0 += 8) {
+        float4 d[8];
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (s0 + j < S) d[j] = load4(dr + (size_t)(s0 + j) * delta_stride + i);
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+            if (s0 + j < S) { x.x += d[j].x; x.y += d[j].y; x.z += d[j].z; x.w += d[j].w; }
+    }
+    if (write_h && S > 0 && mine) *reinterpret_cast<float4*>(hr + i) = x;
+    float ss = x.x * x.x;
+    ss += x.y * x.y;
+    ss += x.z * x.z;
+    ss += x.w * x.w;
+    ss = block_sum(ss, red);
+    if ((int)threadIdx.x < nb) *cluster.map_shared_rank(&sums[rank], threadIdx.x) = ss;
+    cluster.sync();
+    float total = 0.0f;
+    for (int k = 0; k < nb; ++k) total += sums[k];
+    const float scale = 1.0f / sqrtf(total / (float)H + eps);
+    if (mine)
+        Pack4<TOut>::store(y + (size_t)b * H + i, x.x * scale * g.x, x.y * scale * g.y, x.z * scale * g.z,
+                           x.w * scale * g.w);
+}
+
+template <typename TOut>
+static cudaError_t add_rmsnorm_cluster_launch(int n_rows, int nb, int threads, cudaStream_t stream, float* h,
+                                              const float* delta, int S, size_t delta_stride, const float* w,
+                                              float eps, TOut* y, const int* rows, int H, int write_h) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(n_rows * nb);
+    cfg.blockDim = dim3(threads);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[2];
+    attr[0].id = cudaLaunchAttributeClusterDimension;
+    attr[0].val.clusterDim.x = nb;
+    attr[0].val.clusterDim.y = 1;
+    attr[0].val.clusterDim.z = 1;
+    attr[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[1].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = lumen_pdl_enabled() ? 2 : 1;
+    return cudaLaunchKernelEx(&cfg, add_rmsnorm_cluster_kernel<TOut>, h, delta, S, delta_stride, w, eps, y, rows, H,
+                              write_h);
+}
+
 // The same for many rows (prompts) of at most 16 x 512 values: a thread keeps its four groups
 // of four values in registers, so all loads of a row are in flight at once and nothing goes
 // through shared memory. The norm's weight is loaded before the kernel ahead has finished.
@@ -210,6 +290,21 @@ LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long 
         else
             lumen_launch(add_rmsnorm_rows_kernel<float>, dim3(n_rows), dim3(t), 0, stream, h, delta, n_delta,
                          (size_t)delta_stride, w, eps, (float*)y, rows, H, write_h);
+        LUMEN_LAUNCH_CHECK();
+        return 0;
+    }
+    // One row only: measured inside a decode step, the cluster gains 0.7 % of the step at batch 1
+    // (1.255 against 1.265 ms for 12 layers of the 8B shape) and loses 0.6 to 2 % at batch 2 to 16,
+    // where several clusters meet at their barriers at once.
+    if (n_rows == 1 && (H & 3) == 0 && H <= ARN_CLUSTER * 256 * 4) {
+        const int nb = (H / 4 + 255) / 256;                       // blocks a row
+        const int threads = (((H / 4 + nb - 1) / nb + 31) / 32) * 32;
+        cudaError_t e = y_is_bf16
+            ? add_rmsnorm_cluster_launch<__nv_bfloat16>(n_rows, nb, threads, stream, h, delta, n_delta,
+                                                        (size_t)delta_stride, w, eps, (__nv_bfloat16*)y, rows, H, write_h)
+            : add_rmsnorm_cluster_launch<float>(n_rows, nb, threads, stream, h, delta, n_delta, (size_t)delta_stride,
+                                                w, eps, (float*)y, rows, H, write_h);
+        if (e != cudaSuccess) return (int)e;
         LUMEN_LAUNCH_CHECK();
         return 0;
     }

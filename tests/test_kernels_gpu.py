@@ -33,7 +33,7 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("out_dtype", [F32, BF16])
-@pytest.mark.parametrize("N", [13, 301])      # few rows and many: kernels of their own
+@pytest.mark.parametrize("N", [1, 13, 301])   # one row, few rows and many: kernels of their own
 @pytest.mark.parametrize("H,S", [(1000, 0), (80, 1), (4096 + 48, 3), (8192 + 8, 2)])
 def test_add_rmsnorm(out_dtype, H, S, N):
     from lumenllm_b200.ops import kernels as K
@@ -52,12 +52,16 @@ def test_add_rmsnorm(out_dtype, H, S, N):
     assert float(((y - ref).abs() / (1 + ref.abs())).max()) < tol
     assert torch.allclose(hd.cpu(), x, atol=1e-6)             # the stream took the update
     # gathered rows, stream untouched
-    rows = torch.tensor([12, 0, 7], dtype=I32)
+    rows = torch.tensor([12, 0, 7], dtype=I32) % N
     hd2 = dev(h.clone())
     y2 = K.add_rmsnorm(hd2, dev(delta) if S else None, dev(w), eps, out_dtype, rows=dev(rows),
                        write_h=False).cpu().float()
     assert float(((y2 - ref[rows.long()]).abs() / (1 + ref[rows.long()].abs())).max()) < tol
     assert torch.equal(hd2.cpu(), h)
+    # one gathered row (the last row of a prompt before the head)
+    y3 = K.add_rmsnorm(hd2, dev(delta) if S else None, dev(w), eps, out_dtype,
+                       rows=dev(torch.tensor([N - 1], dtype=I32)), write_h=False).cpu().float()
+    assert float(((y3 - ref[N - 1:]).abs() / (1 + ref[N - 1:].abs())).max()) < tol
 
 
 @pytest.mark.parametrize("out_dtype", [F32, BF16])
