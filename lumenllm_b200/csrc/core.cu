@@ -218,22 +218,17 @@ static cudaError_t add_rmsnorm_cluster_launch(int n_rows, int nb, int threads, c
 
 // The same for many rows (prompts) of at most 16 x 512 values: a thread keeps its four groups
 // of four values in registers, so all loads of a row are in flight at once and nothing goes
-// through shared memory. The norm's weight is loaded before the kernel ahead has finished.
+// through shared memory; few registers, so that six blocks of 256 threads share an SM.
 #define ARN_GROUPS 4
 template <typename TOut>
-__global__ void __launch_bounds__(512)
+__global__ void __launch_bounds__(512, 3)
 add_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ delta, int S, size_t delta_stride,
                         const float* __restrict__ w, float eps, TOut* __restrict__ y,
                         const int* __restrict__ rows, int H, int write_h) {
     __shared__ float red[32];
     const int b = blockIdx.x;
-    float4 g[ARN_GROUPS], x[ARN_GROUPS];
-#pragma unroll
-    for (int j = 0; j < ARN_GROUPS; ++j) {
-        const int i = (j * blockDim.x + threadIdx.x) * 4;
-        g[j] = i < H ? load4(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-    }
-    pdl_wait();      // nothing else of this kernel touches global memory before this
+    float4 x[ARN_GROUPS];
+    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
@@ -269,9 +264,11 @@ add_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ delta, 
 #pragma unroll
     for (int j = 0; j < ARN_GROUPS; ++j) {
         const int i = (j * blockDim.x + threadIdx.x) * 4;
-        if (i < H)
-            Pack4<TOut>::store(yr + i, x[j].x * scale * g[j].x, x[j].y * scale * g[j].y, x[j].z * scale * g[j].z,
-                               x[j].w * scale * g[j].w);
+        if (i < H) {
+            const float4 g = load4(w + i);    // the same 16 KB for every row: it stays in L1
+            Pack4<TOut>::store(yr + i, x[j].x * scale * g.x, x[j].y * scale * g.y, x[j].z * scale * g.z,
+                               x[j].w * scale * g.w);
+        }
     }
 }
 
