@@ -607,3 +607,16 @@ def test_fast_attention_kernels_with_drawn_batches(seed):
                              d ** -0.5, tensor_memory=tensor_memory).cpu().float()
         K.check_error_flags()
         assert float((out - ref).abs().max()) < 2 ** -6, ("prefill", tensor_memory, seed, lens, starts, nq, nkv, d, window)
+
+
+@pytest.mark.parametrize("args", [
+    ["gemm_tc", "--m", "8", "--n", "512", "--k", "256"], ["gemm_tc", "--m", "300", "--n", "512", "--k", "256", "--silu"],
+    ["attn_decode", "--batch", "2", "--len", "200"], ["attn_prefill", "--tokens", "256"],
+    ["attn_prefill", "--tokens", "256", "--mma-sync"], ["add_rmsnorm", "--m", "64", "--splits", "2"],
+    ["qk_rope", "--m", "64"], ["argmax", "--m", "2", "--n", "20000"],
+    ["sample", "--m", "2", "--n", "20000", "--top-k", "50", "--top-p", "0.9"]])
+def test_the_micro_benchmark_runs_every_kernel_it_names(args, capsys):
+    from lumenllm_b200 import kbench
+    kbench.main(args + ["--copies", "2", "--reps", "1"])
+    line = capsys.readouterr().out.strip().splitlines()[-1]
+    assert line.startswith(args[0] + ":") and "us per launch" in line
