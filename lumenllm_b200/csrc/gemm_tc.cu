@@ -27,6 +27,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <mutex>
 #include "common.cuh"
 #include "mma_utils.cuh"
 
@@ -720,7 +721,27 @@ static EncodeTiledFn encode_fn() {
 
 // Map of a row-major bfloat16 matrix [rows, K] with boxes of box_rows x 64 values, 128-byte
 // swizzle, zeros outside the matrix.
+// A tensor map is a pure function of (address, rows, K, box rows); encoding one costs the host
+// a microsecond or two, and a step makes some hundreds, nearly all of them for the same weights
+// and the same activation buffers as the step before. A small direct-mapped table keeps them.
+struct MapSlot {
+    const void* base;
+    int rows, K, box_rows;
+    bool full;
+    CUtensorMap map;
+};
+static MapSlot g_maps[1024];
+static std::mutex g_maps_lock;
+
 static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box_rows) {
+    uint64_t h = (uint64_t)(uintptr_t)base * 0x9E3779B97F4A7C15ull;
+    h ^= ((uint64_t)(uint32_t)rows << 32 | (uint32_t)K) * 0xC2B2AE3D27D4EB4Full + (uint64_t)box_rows;
+    MapSlot& slot = g_maps[(h >> 40) & 1023];
+    std::lock_guard<std::mutex> guard(g_maps_lock);
+    if (slot.full && slot.base == base && slot.rows == rows && slot.K == K && slot.box_rows == box_rows) {
+        *map = slot.map;
+        return 0;
+    }
     EncodeTiledFn fn = encode_fn();
     if (!fn) return LUMEN_ERR_UNSUPPORTED;
     cuuint64_t dims[2] = {(cuuint64_t)K, (cuuint64_t)rows};
@@ -730,7 +751,11 @@ static int make_map(CUtensorMap* map, const void* base, int rows, int K, int box
     CUresult r = fn(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, estr,
                     CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
                     CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    return r == CUDA_SUCCESS ? 0 : LUMEN_ERR_BAD_ARGUMENT;
+    if (r != CUDA_SUCCESS) return LUMEN_ERR_BAD_ARGUMENT;
+    slot.base = base; slot.rows = rows; slot.K = K; slot.box_rows = box_rows;
+    slot.map = *map;
+    slot.full = true;
+    return 0;
 }
 
 static int sm_count() {
