@@ -37,6 +37,7 @@
 #define TC_EPI_F32 0
 #define TC_EPI_SILU 1
 #define TC_EPI_ADD 2          // float32, added to what the output holds (two-SM kernel only)
+#define TC_EPI_QKV 3          // heads of 128: q/k RMSNorm, rotation, q out in bfloat16, k and v into the paged cache (two-SM kernel only)
 
 __device__ __forceinline__ void mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -103,6 +104,17 @@ struct TcParams {
     int tma_out;              // two-SM kernel: the output goes through shared memory and the copy engine
     int bn;                   // rows of a B tile: BN, or narrower (a multiple of 16) when that fills the SMs better
     int* err;
+    // EPI_QKV: what the rotary kernel would be given
+    const float* qw;          // norm weights of q and k heads [128], or null
+    const float* kw;
+    const float2* cs;         // (cos, sin) [M, 64], or null without rotation
+    const int* cache_pos;     // [M] place of a row's token in its sequence
+    const int* tok_seq;       // [M] which sequence
+    const int* block_table;   // [B, bt_stride] pages
+    __nv_bfloat16* kcache;    // [pages, nkv, 64, 128], 128-byte swizzled tiles
+    __nv_bfloat16* vcache;
+    float eps;
+    int bt_stride, nq, nkv, rot;
 };
 
 template <int BN, int STAGES, bool SWAP, int EPI>
@@ -439,6 +451,12 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int c0
                  "r"(smem_u32(src)), "r"(c0), "r"(c1)
                  : "memory");
 }
+// Copy of `bytes` (a multiple of 16, both ends 16-byte aligned) from shared to global memory.
+__device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t bytes) {
+    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)),
+                 "r"(bytes)
+                 : "memory");
+}
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 // True in all 128 epilogue threads if it is true in any of them.
 __device__ __forceinline__ bool epi_any(bool pred) {
@@ -465,8 +483,10 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
     unsigned char* smem = smem_raw + ((1024u - (smem_u32(smem_raw) & 1023u)) & 1023u);
     unsigned char* sA = smem;
     unsigned char* sB = smem + STAGES * TC2_TILE_BYTES;
-    unsigned char* sOut = sB + STAGES * TC2_TILE_BYTES;            // two staged output blocks
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + 2 * TC2_OUT_BYTES);
+    constexpr int NOUT = (EPI == TC_EPI_QKV) ? 4 : 2;               // staged output blocks
+    unsigned char* sOut = sB + STAGES * TC2_TILE_BYTES;
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sOut + NOUT * TC2_OUT_BYTES);
+    float* sG = reinterpret_cast<float*>(reinterpret_cast<unsigned char*>(bars) + 256);   // EPI_QKV: the norms' weights, q then k
     uint64_t* full = bars;
     uint64_t* empty = bars + STAGES;
     uint64_t* tfull = bars + 2 * STAGES;
@@ -579,6 +599,11 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
         pdl_wait();
         const int q = warp & 3;
         const int row_in_tile = q * 32 + lane;
+        if (EPI == TC_EPI_QKV) {
+            sG[row_in_tile] = p.qw ? p.qw[row_in_tile] : 1.0f;
+            sG[128 + row_in_tile] = p.kw ? p.kw[row_in_tile] : 1.0f;
+            epi_bar();
+        }
         const uint32_t tempty0 = map_to_cta(smem_u32(tempty), 0);
         const bool issuer = (warp == 2 && lane == 0);    // hands staged blocks to the copy engine
         int acc_it = 0, out_it = 0;
@@ -586,12 +611,150 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             int ta, tb;
             decode(item, ta, tb);
             const int acc = acc_it & 1, aph = (acc_it >> 1) & 1;
+            // EPI_QKV: what a row needs besides the products is fetched while the tensor cores
+            // still work on the tile: its 64 (cos, sin) pairs and, for key and value heads, its page
+            float4 csr[EPI == TC_EPI_QKV ? 32 : 1];
+            int cpos = 0, page = 0;
+            const int a = ta * 256 + (int)rank * 128 + row_in_tile;
+            const bool row_ok = a < p.M;
+            if (EPI == TC_EPI_QKV) {
+                if (p.rot == 128 && row_ok && tb * 2 < p.nq + p.nkv) {
+                    const float4* src = reinterpret_cast<const float4*>(p.cs + (size_t)a * 64);
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) csr[j] = __ldg(src + j);
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; ++j) csr[j] = make_float4(1.f, 0.f, 1.f, 0.f);
+                }
+                if (row_ok && tb * 2 + 1 >= p.nq) {
+                    cpos = p.cache_pos[a];
+                    page = p.block_table[(size_t)p.tok_seq[a] * p.bt_stride + cpos / LUMEN_PAGE];
+                }
+            }
             const bool ok = mbar_wait_timed(&tfull[acc], aph);
             // one decision for all four warps: they meet at barriers further down
             if (epi_any(!ok || *abort_flag != 0)) { *abort_flag = 1; if (lane == 0) atomicExch(p.err, 1); break; }
             tc_fence_after();
             const uint32_t taddr0 = tmem_base + ((uint32_t)(q * 32) << 16) + acc * 256;
             const int row0 = ta * 256 + (int)rank * 128;                // first activation row of this CTA
+            if (EPI == TC_EPI_QKV) {
+                // A tile is two heads of 128 columns, and a thread holds a whole row of each: the
+                // head's RMSNorm and the rotation of the pairs (i, i + 64) stay inside the thread.
+                // A head is staged as two blocks of [128 rows][64 bfloat16] (columns 0-63 and
+                // 64-127); the two heads of a tile have a pair of blocks each, so the second is
+                // staged while the first is being copied out. A query head leaves through two TMA
+                // stores; a key or value head goes row by row, 128 bytes a block, to the row's
+                // place in its page, whose tiles have the same 128-byte swizzle (the row's chunks
+                // are staged in the order of the destination row, so the copy is plain).
+                const int nheads = p.nq + 2 * p.nkv;
+#pragma unroll 1
+                for (int hh = 0; hh < 2; ++hh) {
+                    const int head = tb * 2 + hh;
+                    if (head >= nheads) {     // a last tile of one head: an empty group keeps the count of two a tile
+                        asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                        break;
+                    }
+                    const bool is_q = head < p.nq, is_k = !is_q && head < p.nq + p.nkv;
+                    const uint32_t tcol = taddr0 + hh * 128;
+                    const float* gw = (is_q && p.qw) ? sG : ((is_k && p.kw) ? sG + 128 : nullptr);
+                    unsigned char* blk0 = sOut + (2 * hh) * TC2_OUT_BYTES;
+                    unsigned char* blk1 = blk0 + TC2_OUT_BYTES;
+                    float scale = 1.0f;
+                    if (gw) {
+                        float ss = 0.0f;
+#pragma unroll 1
+                        for (int c = 0; c < 4; ++c) {
+                            float v[32];
+                            tc_ld32(tcol + 32 * c, v);
+#pragma unroll
+                            for (int j = 0; j < 32; ++j) ss += v[j] * v[j];
+                        }
+                        scale = 1.0f / sqrtf(ss / 128.0f + p.eps);
+                    }
+                    // this head's blocks are free once the copies of the tile before have read them:
+                    // at most the other head's group may still be in flight
+                    asm volatile("cp.async.bulk.wait_group.read 1;" ::: "memory");
+                    epi_bar();
+                    int r_dst = row_in_tile;
+                    __nv_bfloat16* dst = nullptr;
+                    if (!is_q && row_ok) {
+                        const int kvh = is_k ? head - p.nq : head - p.nq - p.nkv;
+                        r_dst = cpos % LUMEN_PAGE;
+                        dst = (is_k ? p.kcache : p.vcache) + ((size_t)page * p.nkv + kvh) * (LUMEN_PAGE * 128) +
+                              (size_t)r_dst * 64;
+                    }
+                    const uint32_t swz = (uint32_t)(r_dst & 7);
+                    const bool rotate = (is_q || is_k) && p.rot == 128;
+#pragma unroll
+                    for (int hf = 0; hf < 2; ++hf) {
+                        float lo[32], hi[32];
+                        tc_ld32(tcol + 32 * hf, lo);
+                        tc_ld32(tcol + 64 + 32 * hf, hi);
+                        if (gw) {
+#pragma unroll
+                            for (int j = 0; j < 32; j += 4) {
+                                const float4 g0 = *reinterpret_cast<const float4*>(gw + 32 * hf + j);
+                                const float4 g1 = *reinterpret_cast<const float4*>(gw + 64 + 32 * hf + j);
+                                lo[j] = lo[j] * scale * g0.x; lo[j + 1] = lo[j + 1] * scale * g0.y;
+                                lo[j + 2] = lo[j + 2] * scale * g0.z; lo[j + 3] = lo[j + 3] * scale * g0.w;
+                                hi[j] = hi[j] * scale * g1.x; hi[j + 1] = hi[j + 1] * scale * g1.y;
+                                hi[j + 2] = hi[j + 2] * scale * g1.z; hi[j + 3] = hi[j + 3] * scale * g1.w;
+                            }
+                        }
+                        if (rotate) {       // x'_i = x_i cos - x_{i+64} sin, x'_{i+64} = x_i sin + x_{i+64} cos
+#pragma unroll
+                            for (int j = 0; j < 32; j += 2) {
+                                const float4 c = csr[16 * hf + (j >> 1)];   // (cos, sin) of pairs j and j + 1
+                                const float l0 = lo[j], h0 = hi[j], l1 = lo[j + 1], h1 = hi[j + 1];
+                                lo[j] = l0 * c.x - h0 * c.y; hi[j] = l0 * c.y + h0 * c.x;
+                                lo[j + 1] = l1 * c.z - h1 * c.w; hi[j + 1] = l1 * c.w + h1 * c.z;
+                            }
+                        }
+#pragma unroll
+                        for (int ch = 0; ch < 4; ++ch) {
+                            const uint32_t at = (uint32_t)row_in_tile * 128 + ((((uint32_t)(4 * hf + ch)) ^ swz) << 4);
+                            uint4 w;
+                            w.x = pack_bf16(lo[8 * ch], lo[8 * ch + 1]); w.y = pack_bf16(lo[8 * ch + 2], lo[8 * ch + 3]);
+                            w.z = pack_bf16(lo[8 * ch + 4], lo[8 * ch + 5]); w.w = pack_bf16(lo[8 * ch + 6], lo[8 * ch + 7]);
+                            *reinterpret_cast<uint4*>(blk0 + at) = w;
+                            w.x = pack_bf16(hi[8 * ch], hi[8 * ch + 1]); w.y = pack_bf16(hi[8 * ch + 2], hi[8 * ch + 3]);
+                            w.z = pack_bf16(hi[8 * ch + 4], hi[8 * ch + 5]); w.w = pack_bf16(hi[8 * ch + 6], hi[8 * ch + 7]);
+                            *reinterpret_cast<uint4*>(blk1 + at) = w;
+                        }
+                    }
+                    if (hh == 1 || head + 1 >= nheads) {                // the accumulator has been read out
+                        tc_fence_before();
+                        __syncwarp();
+                        if (lane == 0) mbar_arrive_cluster(tempty0 + acc * 8);
+                    }
+                    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+                    epi_bar();
+                    if (is_q) {
+                        if (issuer && row0 < p.M) {
+                            tma_store_2d(&tmC, head * 128, row0, blk0);
+                            tma_store_2d(&tmC, head * 128 + 64, row0, blk1);
+                        }
+                    } else {
+                        // a warp writes its own 32 rows, four rows an instruction: eight lanes
+                        // take the eight 16-byte chunks of a row's 128 bytes in a block
+                        const unsigned long long dptr = reinterpret_cast<unsigned long long>(dst);
+#pragma unroll 1
+                        for (int i = 0; i < 8; ++i) {
+                            const int src_lane = 4 * i + (lane >> 3);
+                            const unsigned long long d = __shfl_sync(0xffffffffu, dptr, src_lane);
+                            if (d != 0ull) {
+                                const uint32_t at = (uint32_t)(q * 32 + src_lane) * 128 + (uint32_t)(lane & 7) * 16;
+                                __nv_bfloat16* drow = reinterpret_cast<__nv_bfloat16*>(d);
+                                *reinterpret_cast<uint4*>(drow + (lane & 7) * 8) = *reinterpret_cast<const uint4*>(blk0 + at);
+                                *reinterpret_cast<uint4*>(drow + LUMEN_PAGE * 64 + (lane & 7) * 8) =
+                                    *reinterpret_cast<const uint4*>(blk1 + at);
+                            }
+                        }
+                    }
+                    asm volatile("cp.async.bulk.commit_group;" ::: "memory");
+                }
+                continue;
+            }
             if (p.tma_out) {
                 // Through shared memory: each thread puts 32 columns of its row into a staged
                 // block (128 rows of 128 bytes, 16-byte chunk c of row r at c ^ (r & 7), which
@@ -649,7 +812,6 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
                 }
                 continue;
             }
-            const int a = row0 + row_in_tile;                           // activation row m
 #pragma unroll 1
             for (int c0 = 0; c0 < 256; c0 += 16) {
                 float v[16];
@@ -689,7 +851,7 @@ gemm_tc2_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__
             __syncwarp();
             if (lane == 0) mbar_arrive_cluster(tempty0 + acc * 8);
         }
-        if (issuer) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores have landed
+        if (issuer || EPI == TC_EPI_QKV) asm volatile("cp.async.bulk.wait_group 0;" ::: "memory");   // all stores have landed
     }
 
     tc_fence_before();
@@ -894,8 +1056,8 @@ static int make_out_map(CUtensorMap* map, void* base, int rows, int cols, bool f
 template <int EPI>
 static int tc2_launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtensorMap& mc, const TcParams& p,
                       cudaStream_t stream) {
-    constexpr size_t smem = (size_t)TC2_STAGES * 2 * TC2_TILE_BYTES + 2 * TC2_OUT_BYTES +
-                            (2 * TC2_STAGES + 4) * 8 + 16 + 1024;
+    constexpr size_t smem = (size_t)TC2_STAGES * 2 * TC2_TILE_BYTES + (EPI == TC_EPI_QKV ? 4 : 2) * TC2_OUT_BYTES +
+                            256 + (EPI == TC_EPI_QKV ? 1024 : 0) + 1024;
     auto k = gemm_tc2_kernel<EPI>;
     static bool attr_done = false;
     if (!attr_done) {
@@ -1003,4 +1165,57 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
     if ((rc = make_map(&mb, W, N, K, p.bn))) return rc;
     if (epi == TC_EPI_F32) return tc_launch<256, 4, false, TC_EPI_F32>(ma, mb, p, stream);
     return tc_launch<256, 4, false, TC_EPI_SILU>(ma, mb, p, stream);
+}
+
+// The QKV product of a prompt with what follows it folded into the epilogue: per-head RMSNorm of
+// q and k (weights qw, kw of 128 values, or null), rotation of the pairs (i, i + 64) by the
+// (cos, sin) table cs [M, 64] (rot 128; rot 0: none), q out as bfloat16 [M, nq, 128], and k and
+// v written to their rows' places in the paged cache (128-byte swizzled tiles of 64 keys x 128).
+// W: bfloat16 [(nq + 2 nkv) * 128, K], rows in the order q heads, k heads, v heads.
+LUMEN_API int lumen_gemm_tc_qkv_ok(int M, int N, int K, int nq, int nkv, int d, int rot) {
+    return (d == 128 && (rot == 0 || rot == 128) && nq > 0 && nkv > 0 && N == (nq + 2 * nkv) * 128 && K > 0 &&
+            (K & 7) == 0 && !tc_swapped(M, TC_EPI_F32) && tc_two_sm(M, N)) ? 1 : 0;
+}
+
+LUMEN_API int lumen_gemm_tc_qkv(const void* x, const void* W, int M, int N, int K, void* q_out, void* kcache,
+                                void* vcache, const float* qw, const float* kw, float eps, const float* cs, int rot,
+                                const int* cache_pos, const int* tok_seq, const int* block_table, int bt_stride,
+                                int nq, int nkv, int* err, cudaStream_t stream) {
+    if (!lumen_gemm_tc_qkv_ok(M, N, K, nq, nkv, 128, rot)) return LUMEN_ERR_UNSUPPORTED;
+    if (((uintptr_t)x & 15) || ((uintptr_t)W & 15) || ((uintptr_t)q_out & 15) || ((uintptr_t)kcache & 127) ||
+        ((uintptr_t)vcache & 127) || (rot == 128 && (!cs || ((uintptr_t)cs & 15))) || ((uintptr_t)qw & 15) ||
+        ((uintptr_t)kw & 15) || !cache_pos || !tok_seq || !block_table)
+        return LUMEN_ERR_BAD_ARGUMENT;
+    TcParams p = {};
+    p.out_f32 = nullptr;
+    p.out_bf16 = (__nv_bfloat16*)q_out;
+    p.M = M;
+    p.N = N;
+    p.rowsA = M;
+    p.rowsB = N;
+    p.num_kb = (K + TC_BK - 1) / TC_BK;
+    p.splits = 1;
+    p.kb_per_split = p.num_kb;
+    p.tma_out = 1;
+    p.bn = 256;
+    p.err = err;
+    p.qw = qw;
+    p.kw = kw;
+    p.cs = (const float2*)cs;
+    p.cache_pos = cache_pos;
+    p.tok_seq = tok_seq;
+    p.block_table = block_table;
+    p.kcache = (__nv_bfloat16*)kcache;
+    p.vcache = (__nv_bfloat16*)vcache;
+    p.eps = eps;
+    p.bt_stride = bt_stride;
+    p.nq = nq;
+    p.nkv = nkv;
+    p.rot = rot;
+    CUtensorMap ma, mb, mc;
+    int rc;
+    if ((rc = make_map(&ma, x, M, K, TC_BM))) return rc;
+    if ((rc = make_map(&mb, W, N, K, TC_BM))) return rc;
+    if ((rc = make_out_map(&mc, q_out, M, nq * 128, false))) return rc;
+    return tc2_launch<TC_EPI_QKV>(ma, mb, mc, p, stream);
 }

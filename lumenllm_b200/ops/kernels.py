@@ -144,6 +144,52 @@ def qk_norm_rope_store(qkv, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, 
     return q_out
 
 
+def gemm_tc_qkv_takes(M, N, K, nq, nkv, d, rotary_dim) -> bool:
+    """Whether gemm_tc_qkv takes this shape (a prompt-sized product, heads of 128, rotation
+    over the whole head or none)."""
+    return bool(int_fn("gemm_tc", "lumen_gemm_tc_qkv_ok", [c_int] * 7)(
+        int(M), int(N), int(K), int(nq), int(nkv), int(d), int(rotary_dim)))
+
+
+def gemm_tc_qkv(x, w, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, tok_seq, block_table,
+                kcache, vcache, nq, nkv):
+    """The QKV product of a prompt with qk_norm_rope_store folded into its epilogue: x bfloat16
+    [M, K], w bfloat16 [(nq + 2 nkv) * 128, K] (q heads, k heads, v heads); returns q bfloat16
+    [M, nq, 128], normed and rotated, and writes k and v to their places in the swizzled
+    bfloat16 cache. Only where gemm_tc_qkv_takes says so."""
+    require(x, BF16, "gemm_tc_qkv.x")
+    require(w, BF16, "gemm_tc_qkv.w")
+    M, K = x.shape
+    N = w.shape[0]
+    if w.shape[1] != K or not gemm_tc_qkv_takes(M, N, K, nq, nkv, 128, rotary_dim):
+        raise KernelError(f"gemm_tc_qkv does not take [{M}, {K}] x [{N}, {w.shape[1]}] with {nq}+2x{nkv} heads")
+    for t, nm in ((q_norm_w, "q_norm"), (k_norm_w, "k_norm")):
+        if t is not None:
+            require(t, F32, nm)
+            if t.numel() != 128:
+                raise KernelError(f"{nm} weight must have 128 values")
+    if rotary_dim:
+        require(cs, F32, "rope angles")
+        if tuple(cs.shape) != (M, 64, 2):
+            raise KernelError(f"rope angles must be [M, 64, 2], got {tuple(cs.shape)}")
+    for t, nm in ((cache_pos, "cache_pos"), (tok_seq, "tok_seq")):
+        require(t, I32, nm)
+        if t.numel() < M:
+            raise KernelError(f"{nm} shorter than the token count")
+    require(block_table, I32, "block_table")
+    require(kcache, BF16, "kcache")
+    require(vcache, BF16, "vcache")
+    if kcache.shape[1:] != (nkv, 64, 128) or vcache.shape != kcache.shape:
+        raise KernelError("gemm_tc_qkv: caches must be [pages, nkv, 64, 128]")
+    q_out = torch.empty((M, nq, 128), dtype=BF16, device=x.device)
+    f = fn("gemm_tc", "lumen_gemm_tc_qkv",
+           [P, P, c_int, c_int, c_int, P, P, P, P, P, c_float, P, c_int, P, P, P, c_int, c_int, c_int, P, P])
+    check(f(ptr(x), ptr(w), M, N, K, ptr(q_out), ptr(kcache), ptr(vcache), ptr(q_norm_w), ptr(k_norm_w),
+            float(eps), ptr(cs), int(rotary_dim), ptr(cache_pos), ptr(tok_seq), ptr(block_table),
+            block_table.stride(0), nq, nkv, ptr(error_flag(x.device)), stream_ptr()), "gemm_tc_qkv")
+    return q_out
+
+
 def attn_generic(q, kcache, vcache, block_table, tok_seq, tok_pos, window, scale,
                  layout=LAYOUT_LINEAR):
     """Causal attention of N query tokens over the paged cache. q [N, nq, d]."""

@@ -82,6 +82,15 @@ class GQAttention:
     def forward(self, y, ctx, entry, residual=None):
         kc, vc, table = entry.cache()
         writes = entry.writes_cache and not self.shares_cache
+        if (writes and not self.qkv.f32 and entry.layout == K.LAYOUT_SW128 and y.is_contiguous()
+                and K.gemm_tc_qkv_takes(y.shape[0], self.qkv.out_features, self.qkv.in_features, self.nq,
+                                        self.nkv, self.d, self.position.rotary_dim)):
+            # a prompt with heads of 128: norm, rotation and cache write in the product's epilogue
+            q = K.gemm_tc_qkv(y, self.qkv.weight, self.q_norm, self.k_norm, self.qk_eps,
+                              self.position.angles(ctx), self.position.rotary_dim, ctx.cache_pos,
+                              ctx.tok_seq, table, kc, vc, self.nq, self.nkv)
+            out = self.attend(q, kc, vc, table, ctx, entry.layout)
+            return self.o(out.view(-1, self.nq * self.d), split_ok=True, add_to=residual)
         # float32 [N, (nq + 2 nkv) d], possibly as S partial sums
         qkv = self.qkv(y, split_ok=True) if writes else self.q_only(y, split_ok=True)
         nkv_new = self.nkv if writes else 0

@@ -620,3 +620,57 @@ def test_the_micro_benchmark_runs_every_kernel_it_names(args, capsys):
     kbench.main(args + ["--copies", "2", "--reps", "1"])
     line = capsys.readouterr().out.strip().splitlines()[-1]
     assert line.startswith(args[0] + ":") and "us per launch" in line
+
+
+@pytest.mark.parametrize("nq,nkv,H,lens", [(8, 2, 512, [3100, 248]), (5, 1, 256, [2500, 2100, 501]),
+                                           (32, 8, 256, [700, 333])])
+@pytest.mark.parametrize("rot", [128, 0])
+def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nq, nkv, H, lens, rot):
+    """The fused kernel against the plain formulas, and the cache against what the separate
+    kernels write: several sequences that start at different positions, a row count that is no
+    multiple of the tile, an odd number of heads (a last tile of one head)."""
+    from lumenllm_b200.ops import kernels as K
+    g = gen(29)
+    d = 128
+    N = sum(lens)
+    Wn = (nq + 2 * nkv) * d
+    assert K.gemm_tc_qkv_takes(N, Wn, H, nq, nkv, d, rot)
+    starts = [70, 0, 5][:len(lens)]
+    x = torch.randn(N, H, generator=g).to(BF16)
+    w = (torch.randn(Wn, H, generator=g) / math.sqrt(H)).to(BF16)
+    qw = 1 + 0.1 * torch.randn(d, generator=g)
+    kw = 1 + 0.1 * torch.randn(d, generator=g)
+    theta, eps = 50000.0, 1e-6
+    pos = torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(I32)
+    seq = torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).to(I32)
+    width = max((s + n + 63) // 64 for s, n in zip(starts, lens))
+    n_pages = 1 + sum((s + n + 63) // 64 for s, n in zip(starts, lens))
+    perm = torch.randperm(n_pages - 1, generator=g) + 1
+    table = torch.zeros(len(lens), width, dtype=I32)
+    o = 0
+    for b, (s, n) in enumerate(zip(starts, lens)):
+        k_ = (s + n + 63) // 64
+        table[b, :k_] = perm[o:o + k_].to(I32)
+        o += k_
+    kc = torch.zeros(n_pages, nkv, 64, d, dtype=BF16)
+    kcd, vcd = dev(kc), dev(kc.clone())
+    kcd2, vcd2 = dev(kc.clone()), dev(kc.clone())
+    cs = K.rope_table(dev(pos), dev(P.rope_inv_freq(d, theta, d))) if rot else None
+    xd, wd = dev(x), dev(w)
+    q = K.gemm_tc_qkv(xd, wd, dev(qw), dev(kw), eps, cs, rot, dev(pos), dev(seq), dev(table), kcd, vcd, nq, nkv)
+    K.check_error_flags()
+    # the separate kernels on the same product
+    qkv = K.gemm_tc(xd, wd)
+    q2 = K.qk_norm_rope_store(qkv, dev(qw), dev(kw), eps, cs, rot, dev(pos), dev(seq), dev(table), kcd2, vcd2,
+                              nq, nkv, d, BF16, layout=K.LAYOUT_SW128)
+    rel = lambda a, b: float(((a.float() - b.float()).abs() / (1 + b.float().abs())).max())
+    assert rel(q.cpu(), q2.cpu()) < 2 ** -7          # a rounding step of bfloat16 at most
+    assert rel(kcd.cpu(), kcd2.cpu()) < 2 ** -7
+    assert torch.equal(vcd.cpu(), vcd2.cpu())        # values are only rounded
+    assert float(kcd.cpu()[0].float().abs().max()) == 0.0      # page 0 is nobody's
+    # and the plain formulas
+    full = (x.float() @ w.float().T).view(N, nq + 2 * nkv, d)
+    qr = P.rms_norm(full[:, :nq], qw, eps)
+    if rot:
+        qr = P.apply_rope(qr, pos, theta, rot)
+    assert rel(q.cpu(), qr) < 2 ** -7
