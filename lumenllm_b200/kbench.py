@@ -5,6 +5,7 @@
     python -m lumenllm_b200.kbench attn_prefill --tokens 2048 --heads 32 --kv-heads 8 --head-dim 128
     python -m lumenllm_b200.kbench add_rmsnorm --m 2048 --n 4096 [--splits 9]
     python -m lumenllm_b200.kbench qk_rope --m 2048 --heads 32 --kv-heads 8 --head-dim 128
+    python -m lumenllm_b200.kbench gemm_qkv --m 2048 --k 4096 --heads 32 --kv-heads 8
     python -m lumenllm_b200.kbench argmax --m 8 --n 151936
     python -m lumenllm_b200.kbench sample --m 8 --n 151936 [--top-k 50] [--top-p 0.9]
 
@@ -57,7 +58,7 @@ def _paged(B, length, nkv, d, dev):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="kbench")
     ap.add_argument("kernel", choices=["gemm_tc", "attn_decode", "attn_prefill",
-                                       "add_rmsnorm", "qk_rope", "argmax", "sample"])
+                                       "add_rmsnorm", "qk_rope", "gemm_qkv", "argmax", "sample"])
     ap.add_argument("--splits", type=int, default=1, help="add_rmsnorm: partial sums to add")
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
@@ -124,7 +125,7 @@ def main(argv=None):
             fns = [lambda l=l: K.sample(l, opts, tk) for l in lgs]
         us = _time(fns, a.reps)
         note = f"{a.m * a.n * 4 / us / 1e3:.0f} GB/s"
-    else:
+    elif a.kernel == "qk_rope":
         nh = a.heads + 2 * a.kv_heads
         xs = [torch.randn(a.m, nh * a.head_dim, device=dev) for _ in range(a.copies)]
         kc, vc, table = _paged(1, a.m, a.kv_heads, a.head_dim, dev)
@@ -138,6 +139,21 @@ def main(argv=None):
                for x in xs]
         us = _time(fns, a.reps)
         note = f"{a.m * nh * a.head_dim * 6 / us / 1e3:.0f} GB/s"
+    else:
+        # the QKV product of a prompt with norm, rotation and cache write in its epilogue
+        nh = a.heads + 2 * a.kv_heads
+        ws = [(torch.randn(nh * 128, a.k, device=dev) / math.sqrt(a.k)).to(bf) for _ in range(a.copies)]
+        x = torch.randn(a.m, a.k, device=dev).to(bf)
+        kc, vc, table = _paged(1, a.m, a.kv_heads, 128, dev)
+        pos = torch.arange(a.m, dtype=torch.int32, device=dev)
+        seq = torch.zeros(a.m, dtype=torch.int32, device=dev)
+        inv = 1.0 / (1e6 ** (torch.arange(0, 128, 2, dtype=torch.float32) / 128))
+        cs = K.rope_table(pos, inv.to(dev))
+        wn = torch.ones(128, device=dev)
+        fns = [lambda w=w: K.gemm_tc_qkv(x, w, wn, wn, 1e-6, cs, 128, pos, seq, table, kc, vc, a.heads, a.kv_heads)
+               for w in ws]
+        us = _time(fns, a.reps)
+        note = f"{2.0 * a.m * nh * 128 * a.k / us / 1e6:.1f} TFLOP/s"
     K.check_error_flags()
     print(f"{a.kernel}: {us:.1f} us per launch  {note}")
     return 0

@@ -613,7 +613,7 @@ def test_fast_attention_kernels_with_drawn_batches(seed):
     ["gemm_tc", "--m", "8", "--n", "512", "--k", "256"], ["gemm_tc", "--m", "300", "--n", "512", "--k", "256", "--silu"],
     ["attn_decode", "--batch", "2", "--len", "200"], ["attn_prefill", "--tokens", "256"],
     ["attn_prefill", "--tokens", "256", "--mma-sync"], ["add_rmsnorm", "--m", "64", "--splits", "2"],
-    ["qk_rope", "--m", "64"], ["argmax", "--m", "2", "--n", "20000"],
+    ["qk_rope", "--m", "64"], ["gemm_qkv", "--m", "2048", "--k", "256"], ["argmax", "--m", "2", "--n", "20000"],
     ["sample", "--m", "2", "--n", "20000", "--top-k", "50", "--top-p", "0.9"]])
 def test_the_micro_benchmark_runs_every_kernel_it_names(args, capsys):
     from lumenllm_b200 import kbench
