@@ -451,12 +451,6 @@ __device__ __forceinline__ void tma_reduce_add_2d(const CUtensorMap* map, int c0
                  "r"(smem_u32(src)), "r"(c0), "r"(c1)
                  : "memory");
 }
-// Copy of `bytes` (a multiple of 16, both ends 16-byte aligned) from shared to global memory.
-__device__ __forceinline__ void bulk_store(void* dst, const void* src, uint32_t bytes) {
-    asm volatile("cp.async.bulk.global.shared::cta.bulk_group [%0], [%1], %2;" ::"l"(dst), "r"(smem_u32(src)),
-                 "r"(bytes)
-                 : "memory");
-}
 __device__ __forceinline__ void epi_bar() { asm volatile("bar.sync 1, 128;" ::: "memory"); }
 // True in all 128 epilogue threads if it is true in any of them.
 __device__ __forceinline__ bool epi_any(bool pred) {
