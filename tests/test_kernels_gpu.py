@@ -674,3 +674,57 @@ def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nq, nkv,
     if rot:
         qr = P.apply_rope(qr, pos, theta, rot)
     assert rel(q.cpu(), qr) < 2 ** -7
+
+
+@pytest.mark.parametrize("seed", range(8))
+def test_drawn_qkv_products_with_their_epilogue(seed):
+    """Heads, groups, width, sequences, where they start, norm weights or none, rotation or none,
+    drawn at random: the fused kernel against the product and the rotary kernel one after the
+    other (queries and keys within a rounding step of bfloat16, values and untouched pages
+    bit for bit)."""
+    import random
+    from lumenllm_b200.ops import kernels as K
+    rng = random.Random(400 + seed)
+    g = gen(400 + seed)
+    d = 128
+    while True:
+        nkv = rng.choice([1, 2, 3, 4, 8])
+        nq = nkv * rng.choice([1, 2, 3, 4, 8])
+        H = 8 * rng.randint(4, 64)
+        total = rng.randint(1200, 7000)
+        rot = rng.choice([128, 128, 0])
+        if K.gemm_tc_qkv_takes(total, (nq + 2 * nkv) * d, H, nq, nkv, d, rot):
+            break
+    nseq = rng.randint(1, 5)
+    cuts = sorted(rng.sample(range(1, total), nseq - 1))
+    lens = [b - a for a, b in zip([0] + cuts, cuts + [total])]
+    starts = [rng.choice([0, 0, rng.randint(1, 300)]) for _ in lens]
+    x = dev(torch.randn(total, H, generator=g).to(BF16))
+    w = dev((torch.randn((nq + 2 * nkv) * d, H, generator=g) / math.sqrt(H)).to(BF16))
+    normed = rng.random() < 0.8
+    qw = dev(1 + 0.1 * torch.randn(d, generator=g)) if normed else None
+    kw = dev(1 + 0.1 * torch.randn(d, generator=g)) if normed else None
+    pos = dev(torch.cat([torch.arange(s, s + n) for s, n in zip(starts, lens)]).to(I32))
+    seq = dev(torch.cat([torch.full((n,), b) for b, n in enumerate(lens)]).to(I32))
+    width = max((s + n + 63) // 64 for s, n in zip(starts, lens))
+    n_pages = 1 + sum((s + n + 63) // 64 for s, n in zip(starts, lens))
+    perm = torch.randperm(n_pages - 1, generator=g) + 1
+    table = torch.zeros(len(lens), width, dtype=I32)
+    o = 0
+    for b, (s, n) in enumerate(zip(starts, lens)):
+        k_ = (s + n + 63) // 64
+        table[b, :k_] = perm[o:o + k_].to(I32)
+        o += k_
+    table = dev(table)
+    kc, vc, kc2, vc2 = (dev(torch.zeros(n_pages, nkv, 64, d, dtype=BF16)) for _ in range(4))
+    cs = K.rope_table(pos, dev(P.rope_inv_freq(d, 50000.0, d))) if rot else None
+    q = K.gemm_tc_qkv(x, w, qw, kw, 1e-6, cs, rot, pos, seq, table, kc, vc, nq, nkv)
+    K.check_error_flags()
+    q2 = K.qk_norm_rope_store(K.gemm_tc(x, w), qw, kw, 1e-6, cs, rot, pos, seq, table, kc2, vc2, nq, nkv, d,
+                              BF16, layout=K.LAYOUT_SW128)
+    rel = lambda a, b: float(((a.float() - b.float()).abs() / (1 + b.float().abs())).max())
+    what = (seed, nq, nkv, H, lens, starts, rot, normed)
+    assert rel(q, q2) < 2 ** -7, what
+    assert rel(kc, kc2) < 2 ** -7, what
+    assert torch.equal(vc, vc2), what
+    assert float(kc[0].float().abs().max()) == 0.0, what
