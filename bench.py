@@ -2,10 +2,15 @@
 """Benchmark of lumenllm_b200 on one B200: decode tokens per second of a
 Qwen3-8B-shaped model (random bfloat16 weights, synthetic token ids) at batch 8,
 with prefill of 2,048 tokens, batch-1 and batch-64 decode, an end-to-end number
-through the Python entry point, and the HBM roofline of the decode step.
+through the Python entry point, time to the first token of short prompts, and the
+HBM roofline of the decode step.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+                    [--shape 8b|14b|32b] [--timings]
 
+`--shape` runs the same measurement at the two larger workloads (their batch, prompt
+lengths, context and sampling); `--timings` adds, from a separate pass that is not
+timed as a whole, each kernel class's share of a decode step and of a prompt step.
 One JSON line goes to standard output. More than one GPU is not built: the
 program says so and exits with 2.
 """
@@ -21,14 +26,28 @@ import time
 ROOT = os.path.dirname(os.path.abspath(__file__))
 sys.path.insert(0, ROOT)
 
-# BASELINE.json configs[2]: the Qwen3-8B shape.
-SHAPE = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_hidden_layers=36,
-             hidden_size=4096, num_attention_heads=32, num_key_value_heads=8, head_dim=128,
-             intermediate_size=12288, vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6,
-             max_position_embeddings=40960, tie_word_embeddings=False)
+COMMON = dict(architectures=["Qwen3ForCausalLM"], model_type="qwen3", num_key_value_heads=8, head_dim=128,
+              vocab_size=151936, rope_theta=1000000.0, rms_norm_eps=1e-6, max_position_embeddings=40960,
+              tie_word_embeddings=False)
+# The benchmark shape (Qwen3-8B) and the two larger workloads: layer sizes, and per workload the
+# batch, the range of prompt lengths, the context length and how tokens are chosen.
+WORKLOADS = {
+    "8b": dict(model=dict(COMMON, num_hidden_layers=36, hidden_size=4096, num_attention_heads=32,
+                          intermediate_size=12288),
+               batch=8, prompt=(1024, 2048), context=4096, temperature=0.0),
+    "14b": dict(model=dict(COMMON, num_hidden_layers=40, hidden_size=5120, num_attention_heads=40,
+                           intermediate_size=17408),
+                batch=16, prompt=(256, 6144), context=8192, temperature=0.0),
+    "32b": dict(model=dict(COMMON, num_hidden_layers=64, hidden_size=5120, num_attention_heads=64,
+                           intermediate_size=25600),
+                batch=8, prompt=(128, 2048), context=4096, temperature=0.7),
+}
+SHAPE = WORKLOADS["8b"]["model"]
 CONTEXT = 4096
 PROMPT_LO, PROMPT_HI = 1024, 2048
 PREFILL_TOKENS = 2048
+TEMPERATURE = 0.0
+SAMPLING_SEED = 1234
 
 
 def peaks():
@@ -98,31 +117,42 @@ def model_numbers(cfg, layers):
             "kv_bytes_per_token": 2 * layers * kvw * 2}
 
 
+def sampling_for(B):
+    """Options of the B sequences and a function step -> their uniform numbers: greedy, or at the
+    workload's temperature with one seeded stream of uniforms per sequence (made on the host and
+    passed to the device sampler every step, as generation does)."""
+    from lumenllm_b200.sampling import SamplingConfig, uniform
+    if TEMPERATURE <= 0.0:
+        return [SamplingConfig()] * B, (lambda step: [0.0] * B)
+    cfgs = [SamplingConfig(temperature=TEMPERATURE, seed=SAMPLING_SEED + i) for i in range(B)]
+    return cfgs, (lambda step: [uniform(SAMPLING_SEED + i, 0, step) for i in range(B)])
+
+
 def decode_run(eng, B, steps, warmup, seed):
-    """Prefills B prompts (lengths uniform in [PROMPT_LO, PROMPT_HI]), then decodes greedily
+    """Prefills B prompts (lengths uniform in [PROMPT_LO, PROMPT_HI]), then decodes
     with the sampled tokens fed back on the device. Returns per-step ms and bytes read."""
     import torch
     from lumenllm_b200 import StepEntry
-    from lumenllm_b200.sampling import SamplingConfig
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(PROMPT_LO, PROMPT_HI + 1, (B,), generator=g).tolist()
     prompts = [torch.randint(0, eng.vocab_size, (n,), generator=g).tolist() for n in lens]
     slots = [eng.alloc_slot() for _ in range(B)]
     logits = eng.step([StepEntry(s, p, [len(p) - 1]) for s, p in zip(slots, prompts)])
-    cfgs = [SamplingConfig()] * B
-    tok = eng.sampler.pick(logits, cfgs, [0.0] * B)
+    cfgs, uniforms = sampling_for(B)
+    tok = eng.sampler.pick(logits, cfgs, uniforms(0))
     entries = [(s, [0]) for s in slots]
-    for _ in range(warmup):
-        tok = eng.run_device(entries, cfgs, [0.0] * B, tokens_on_device=tok)
+    for k in range(warmup):
+        tok = eng.run_device(entries, cfgs, uniforms(1 + k), tokens_on_device=tok)
     torch.cuda.synchronize()
     ev0, ev1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     t0 = time.perf_counter()
     ev0.record()
-    for _ in range(steps):
-        tok = eng.run_device(entries, cfgs, [0.0] * B, tokens_on_device=tok)
+    for k in range(steps):
+        tok = eng.run_device(entries, cfgs, uniforms(1 + warmup + k), tokens_on_device=tok)
     ev1.record()
     torch.cuda.synchronize()
     t1 = time.perf_counter()
+    eng.check_kernels()
     ms = ev0.elapsed_time(ev1) / steps
     mean_len = sum(lens) / B + warmup + steps / 2
     launches = getattr(eng.graphs, "last", None)
@@ -131,6 +161,92 @@ def decode_run(eng, B, steps, warmup, seed):
         eng.free_slot(s)
     return {"ms": ms, "mean_len": mean_len, "window": (t0, t1), "kernels_per_step": per,
             "tok_s": B * 1000.0 / ms}
+
+
+def first_token_run(eng, n_tokens, runs=7):
+    """Milliseconds from the call with a prompt of n_tokens host tokens to its first sampled
+    token on the host (median of `runs`, after two untimed ones)."""
+    import torch
+    g = torch.Generator().manual_seed(100 + n_tokens)
+    prompt = torch.randint(0, eng.vocab_size, (n_tokens,), generator=g).tolist()
+    cfgs, uniforms = sampling_for(1)
+    times = []
+    for it in range(2 + runs):
+        s = eng.alloc_slot()
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        eng.run([(s, prompt)], cfgs, uniforms(0))
+        times.append((time.perf_counter() - t0) * 1e3)
+        eng.free_slot(s)
+    return statistics.median(times[2:])
+
+
+def timings_pass(eng, B, model_cfg):
+    """Each kernel class's share of one decode step at batch B and of one 2,048-token prompt
+    step, from a pass of its own: every launch is bracketed by two CUDA events (which also
+    keeps kernels from overlapping, so the shares are of the sum of the kernels' own times,
+    not of the step's time). After crates/aegisllm-cuda/src/executor/prefill/timings.rs:1-39."""
+    import torch
+    from lumenllm_b200 import StepEntry
+    from lumenllm_b200.ops import native
+    H, I = model_cfg["hidden_size"], model_cfg["intermediate_size"]
+    qw = model_cfg["num_attention_heads"] * model_cfg["head_dim"]
+    kvw = model_cfg["num_key_value_heads"] * model_cfg["head_dim"]
+    products = {(qw + 2 * kvw, H): "qkv", (H, qw): "o", (2 * I, H): "gate_up", (H, I): "down",
+                (model_cfg["vocab_size"], H): "head"}
+    if qw == I:      # cannot happen for the shapes here; keeps the table honest if it does
+        products[(H, qw)] = "o_or_down"
+    names = {"lumen_add_rmsnorm": "norm", "lumen_qk_norm_rope_store": "qk_norm_rope_store",
+             "lumen_rope_table": "rope_table", "lumen_silu_mul": "silu_mul", "lumen_embed": "embed",
+             "lumen_attn_decode": "attention", "lumen_attn_prefill_tc": "attention",
+             "lumen_attn_prefill": "attention", "lumen_attn_generic": "attention",
+             "lumen_argmax": "sampling", "lumen_sample": "sampling", "lumen_gemm_tc_qkv": "qkv"}
+
+    def label(name, args):
+        if name == "lumen_gemm_tc":
+            return products.get((int(args[4]), int(args[5])), "other_product")
+        return names.get(name, name)
+
+    def shares(run):
+        rec = []
+        native.instrument(lambda name, args: rec.append([label(name, args), torch.cuda.Event(enable_timing=True),
+                                                         torch.cuda.Event(enable_timing=True)]) or rec[-1])
+        try:
+            run()
+            torch.cuda.synchronize()
+        finally:
+            native.instrument(None)
+        total, by = 0.0, {}
+        for lab, e0, e1 in rec:
+            ms = e0.elapsed_time(e1)
+            by[lab] = by.get(lab, 0.0) + ms
+            total += ms
+        out = {k: round(v / total, 4) for k, v in sorted(by.items(), key=lambda kv: -kv[1])}
+        out["sum_ms"] = round(total, 3)
+        out["launches"] = len(rec)
+        return out
+
+    g = torch.Generator().manual_seed(5)
+    lens = torch.randint(PROMPT_LO, PROMPT_HI + 1, (B,), generator=g).tolist()
+    slots = [eng.alloc_slot() for _ in range(B)]
+    eng.step([StepEntry(s, torch.randint(0, eng.vocab_size, (n,), generator=g).tolist(), [])
+              for s, n in zip(slots, lens)])
+    cfgs, uniforms = sampling_for(B)
+    was = eng.use_graphs
+    eng.use_graphs = False            # launch by launch, so that every kernel can be bracketed
+    try:
+        for _ in range(2):
+            eng.run_device([(s, [1]) for s in slots], cfgs, uniforms(0))
+        decode = shares(lambda: eng.run_device([(s, [1]) for s in slots], cfgs, uniforms(1)))
+    finally:
+        eng.use_graphs = was
+    for s in slots:
+        eng.free_slot(s)
+    prompt = torch.randint(0, eng.vocab_size, (PREFILL_TOKENS,), generator=g).tolist()
+    s = eng.alloc_slot()
+    prefill = shares(lambda: eng.step([StepEntry(s, prompt, [PREFILL_TOKENS - 1])]))
+    eng.free_slot(s)
+    return {"decode": decode, "prefill": prefill}
 
 
 def prefill_run(eng, warmup, runs=5):
@@ -164,7 +280,8 @@ def e2e_run(built, B, steps, seed):
     g = torch.Generator().manual_seed(seed)
     lens = torch.randint(PROMPT_LO, PROMPT_HI + 1, (B,), generator=g).tolist()
     prompts = [torch.randint(0, built.engine.vocab_size, (n,), generator=g).tolist() for n in lens]
-    reqs = [GenerateRequest(p, steps + 1) for p in prompts]
+    cfgs, _ = sampling_for(B)
+    reqs = [GenerateRequest(p, steps + 1, c) for p, c in zip(prompts, cfgs)]
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     outs = built.generate(reqs, eos_token_ids=[], max_batch=B)
@@ -181,18 +298,26 @@ def main() -> int:
     ap.add_argument("--steps", type=int, default=128)
     ap.add_argument("--warmup", type=int, default=8)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=SHAPE["num_hidden_layers"],
+    ap.add_argument("--shape", default="8b", choices=sorted(WORKLOADS),
+                    help="layer sizes and workload (default: the benchmark configuration, 8b)")
+    ap.add_argument("--layers", type=int, default=None,
                     help="fewer layers than the shape has, for small memory (named in config)")
-    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
-    ap.add_argument("--context", type=int, default=CONTEXT,
-                    help="context length (default: the baseline configuration's)")
-    ap.add_argument("--prompt-len", default=f"{PROMPT_LO}:{PROMPT_HI}", metavar="LO:HI",
+    ap.add_argument("--timings", action="store_true",
+                    help="add each kernel class's share of a decode and of a prompt step")
+    ap.add_argument("--context", type=int, default=None,
+                    help="context length (default: the workload's)")
+    ap.add_argument("--prompt-len", default=None, metavar="LO:HI",
                     help="prompt lengths are drawn uniformly from this range")
     args = ap.parse_args()
-    globals()["CONTEXT"] = args.context
-    lo, _, hi = args.prompt_len.partition(":")
+    wl = WORKLOADS[args.shape]
+    shape = wl["model"]
+    globals()["CONTEXT"] = args.context or wl["context"]
+    lo, _, hi = (args.prompt_len or f"{wl['prompt'][0]}:{wl['prompt'][1]}").partition(":")
     globals()["PROMPT_LO"], globals()["PROMPT_HI"] = int(lo), int(hi or lo)
+    globals()["TEMPERATURE"] = wl["temperature"]
+    layers = args.layers or shape["num_hidden_layers"]
     if not 1 <= PROMPT_LO <= PROMPT_HI or PROMPT_HI + 64 + max(3, args.warmup) + max(1, args.steps) + 64 > CONTEXT:
         print("bench.py: prompts, warm-up and steps must fit the context", file=sys.stderr)
         return 2
@@ -212,12 +337,12 @@ def main() -> int:
     from lumenllm_b200.config import SamplingDefaults
     from lumenllm_b200.ops import native
     pk = peaks()
-    cfg = dict(SHAPE, num_hidden_layers=args.layers)
-    B = args.batch
+    cfg = dict(shape, num_hidden_layers=layers)
+    B = args.batch or wl["batch"]
     top_b = B if args.no_points else max(B, 64)
     max_tokens = max(B * CONTEXT, top_b * (PROMPT_HI + 64 + warmup + steps + 64))
-    nums = model_numbers(cfg, args.layers)
-    need = max_tokens * nums["kv_bytes_per_token"] + 2 * (nums["layer_params"] + nums["head_params"])
+    nums = model_numbers(cfg, layers)
+    need = max_tokens * nums["kv_bytes_per_token"] + 2 * (nums["layer_params"] + 2 * nums["head_params"])
     if need > 165e9:
         print(f"bench.py: {need / 1e9:.0f} GB of weights and cache do not fit; use --no-points, a "
               "smaller --batch or --context, or fewer --layers", file=sys.stderr)
@@ -225,7 +350,7 @@ def main() -> int:
     eng = Engine.from_random(cfg, seed=0, std=0.02, dtype="bfloat16", max_tokens=max_tokens,
                              max_slots=max(top_b, 8), context_size=CONTEXT)
     eng.graphs.min_width = CONTEXT // 64
-    built = BuiltEngine(eng, SamplingDefaults(), B)
+    built = BuiltEngine(eng, SamplingDefaults(temperature=TEMPERATURE, seed=SAMPLING_SEED), B)
     clocks = Clocks()
     clocks.start()
 
@@ -233,6 +358,7 @@ def main() -> int:
     # a GEMM reaches before the power cap settles the clocks), so it runs before the long
     # decode loops have warmed the GPU
     pre_ms, pre_windows = prefill_run(eng, warmup=3)
+    ttft = {str(n): round(first_token_run(eng, n), 3) for n in (128, 512)}
 
     launches0 = native.launches
     main_run = decode_run(eng, B, steps, warmup, seed=1)
@@ -244,7 +370,7 @@ def main() -> int:
 
     T = PREFILL_TOKENS
     flops = 2 * T * nums["layer_params"] + 2 * nums["head_params"] \
-        + args.layers * 2 * T * T * cfg["head_dim"] * cfg["num_attention_heads"]
+        + layers * 2 * T * T * cfg["head_dim"] * cfg["num_attention_heads"]
     pre_frac = flops / (pre_ms * 1e-3) / (pk["bf16_tflops"] * 1e12)
 
     # three runs, the median: a run is a quarter of a second, and host jitter shows in it
@@ -261,24 +387,29 @@ def main() -> int:
             windows.append(r["window"])
     time.sleep(0.3)
     clocks.stop()
-    meta_bytes = 4 * (9 * 4 * ((B + 3) // 4 + 1) + B * (CONTEXT // 64))
+    timings = timings_pass(eng, B, cfg) if args.timings else None
+    sampled = TEMPERATURE > 0.0
+    # per step and host to device: the step's metadata, and with sampling its options and
+    # uniform numbers; device to host: the sampled tokens and the kernels' error flag
+    meta_bytes = 4 * (9 * 4 * ((B + 3) // 4 + 1) + B * (CONTEXT // 64)) + (20 * B if sampled else 0)
     out = {
         "metric": "decode_tokens_per_s", "value": round(main_run["tok_s"], 1), "unit": "tokens/s",
         "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": round(ms, 4),
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic", "impl": "ours",
-        "config": {"model": "qwen3-8b-shape", "layers": args.layers,
-                   "layers_of_shape": SHAPE["num_hidden_layers"], "hidden": cfg["hidden_size"],
+        "config": {"model": f"qwen3-{args.shape}-shape", "layers": layers,
+                   "layers_of_shape": shape["num_hidden_layers"], "hidden": cfg["hidden_size"],
                    "heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
                    "vocab": cfg["vocab_size"], "rope_theta": cfg["rope_theta"],
                    "rms_norm_eps": cfg["rms_norm_eps"], "tied_head": False, "global_batch": B,
                    "seq_len": CONTEXT, "prompt_len": f"{PROMPT_LO}..{PROMPT_HI}",
-                   "parallelism": "single", "weights": "random N(0,0.02)", "cache_page": 64,
+                   "parallelism": "single", "weights": "random N(0,0.02)",
+                   "sampling": f"temperature {TEMPERATURE} seeded" if sampled else "greedy",
                    "l2": "inputs_larger_than_l2", "peaks": pk["source"]},
         "clocks": clocks.summary(windows),
         "e2e": {"value": round(e2e["tok_s"], 1), "unit": "tokens/s",
-                "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * B},
+                "h2d_bytes_per_step": meta_bytes, "d2h_bytes_per_step": 4 * B + 4},
         "gpu_launches": int(main_run["kernels_per_step"] * steps) or int(eager_launches),
         "prefill": {"value": round(T / (pre_ms * 1e-3), 1), "tokens": T, "ms": round(pre_ms, 3),
                     "frac": round(pre_frac, 4)},
@@ -286,7 +417,10 @@ def main() -> int:
                      "unit": "GB/s", "frac": round(achieved / pk["hbm_gbs"], 4)},
         "points": points,
         "points_roofline_frac": points_frac,     # the same bytes-over-time figure as "roofline"
+        "first_token_ms": ttft,                  # prompts of 128 and 512 tokens, host to host
     }
+    if timings is not None:
+        out["timings"] = timings
     print(json.dumps(out))
     return 0
 

@@ -4,9 +4,10 @@ tokens out, through hand-written CUDA kernels."""
 from .config import ConfigError, Qwen3Config, config_from_dict, load_config
 from .engine import (BuiltEngine, Engine, EngineConfig, GenerateOutput, GenerateRequest, StepEntry,
                      StepError, build)
+from .ops.native import KernelError
 from .sampling import SamplingConfig
 
 __version__ = "0.1.0"
 __all__ = ["ConfigError", "Qwen3Config", "config_from_dict", "load_config", "BuiltEngine", "Engine",
            "EngineConfig", "GenerateOutput", "GenerateRequest", "StepEntry", "StepError", "build",
-           "SamplingConfig"]
+           "SamplingConfig", "KernelError"]

@@ -24,9 +24,10 @@ from typing import Dict, List, Optional, Tuple
 import numpy as np
 import torch
 
+from ..csrc.build import page_size
 from .slots import CacheError, CacheFull, PagePool, SlotAllocator
 
-PAGE = 64
+PAGE = page_size()      # tokens per page: LUMEN_PAGE of csrc/common.cuh
 LAYOUT_LINEAR, LAYOUT_SW128 = 0, 1
 
 
@@ -122,14 +123,18 @@ class CacheGroup:
 
 class StateStore:
     """Per-sequence state of fixed size: for each entry that declares a shape, a
-    tensor [max_slots, *shape], zeroed when a slot is handed out. It is never
-    indexed by position and never grows. (The reference keeps such state per
-    layer for its recurrent mixers: executor/state.rs:640-648.)"""
+    tensor [max_slots + 1, *shape], zeroed when a slot is handed out. It is never
+    indexed by position and never grows. Row `pad_row` (the last) belongs to no
+    sequence: the padding rows of a captured step read and write it, as they write
+    page 0 of the cache, so that a mixer which indexes its state by `seq_slot` on the
+    device touches no live sequence's state for them. (The reference keeps such state
+    per layer for its recurrent mixers: executor/state.rs:640-648.)"""
 
     def __init__(self, shapes: Dict[int, Tuple[Tuple[int, ...], torch.dtype]], max_slots: int, device):
+        self.pad_row = max_slots
         self.tensors: Dict[int, torch.Tensor] = {}
         for entry, (shape, dtype) in shapes.items():
-            self.tensors[entry] = torch.zeros((max_slots, *shape), dtype=dtype, device=device)
+            self.tensors[entry] = torch.zeros((max_slots + 1, *shape), dtype=dtype, device=device)
 
     def zero_slot(self, slot: int) -> None:
         for t in self.tensors.values():

@@ -13,7 +13,7 @@ from __future__ import annotations
 from dataclasses import dataclass, field
 from typing import Any, Dict, Optional, Tuple
 
-from .registry import register_architecture
+from .registry import eos_ids_of, register_architecture
 from .spec import ConfigError, LayerSpec, ModelSpec, PartSpec, ScheduleEntry
 
 _REQUIRED = ("hidden_size", "num_hidden_layers", "num_attention_heads", "vocab_size",
@@ -119,13 +119,14 @@ class Qwen3Config:
             if isinstance(win, bool) or not isinstance(win, int) or win <= 0:
                 raise ConfigError("config.json: a sliding window is switched on but "
                                   f"'sliding_window' is {win!r}")
-        eos = d.get("eos_token_id")
-        if eos is None:
-            eos_ids: Tuple[int, ...] = ()
-        elif isinstance(eos, int):
-            eos_ids = (eos,)
-        else:
-            eos_ids = tuple(int(x) for x in eos)
+            if lt is None and d.get("max_window_layers") is None:
+                # which layers get the window is the file's to say; the reference ignores
+                # windows for this family (crates/aegisllm-base/src/model/qwen3.rs:55-61),
+                # so there is no default of its own to take
+                raise ConfigError("config.json: use_sliding_window is on, but neither "
+                                  "'layer_types' nor 'max_window_layers' says which layers "
+                                  "have the window")
+        eos_ids: Tuple[int, ...] = eos_ids_of(d.get("eos_token_id"), "config.json")
         dtype = d.get("torch_dtype", d.get("dtype", "bfloat16"))
         known = set(cls.__dataclass_fields__) | {"eos_token_id", "dtype", "hidden_activation",
                                                   "rope_scaling", "rope_parameters"}
@@ -217,7 +218,8 @@ class Qwen3Config:
                                             "weight_offset": 0.0}, prefix="model.norm"),
             head=PartSpec("linear_head", {"vocab_size": self.vocab_size, "hidden_size": H,
                                           "tied_to": "model.embed_tokens.weight"
-                                          if self.tie_word_embeddings else None},
+                                          if self.tie_word_embeddings else None,
+                                          "falls_back_to": "model.embed_tokens.weight"},
                           prefix="lm_head"),
             eos_token_ids=self.eos_token_ids,
         )

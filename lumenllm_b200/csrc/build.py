@@ -47,6 +47,16 @@ class BuildError(RuntimeError):
     pass
 
 
+def page_size() -> int:
+    """Tokens per cache page: the value of LUMEN_PAGE in common.cuh, the one place where the
+    number is written. The Python side (cache, generation loop, metadata) reads it here."""
+    import re
+    m = re.search(r"^#define\s+LUMEN_PAGE\s+(\d+)\s*$", (CSRC / "common.cuh").read_text(), re.M)
+    if not m:
+        raise BuildError("common.cuh does not define LUMEN_PAGE")
+    return int(m.group(1))
+
+
 def _nvcc() -> str:
     for cand in (os.environ.get("NVCC"), shutil.which("nvcc"), "/usr/local/cuda/bin/nvcc"):
         if cand and Path(cand).exists():
@@ -97,7 +107,7 @@ def _compile(module: str, out_dir: Path) -> Path:
     srcs, _ = MODULES[module]
     final = out_dir / f"lumen_{module}.{_digest(module)}.so"
     tmp = out_dir / f".lumen_{module}.{os.getpid()}.{threading.get_ident()}.tmp.so"
-    cmd = [_nvcc(), *NVCC_FLAGS, f'-DLUMEN_MODULE="{module}"', "-I", str(CSRC), "-o", str(tmp)] + [str(CSRC / s) for s in srcs]
+    cmd = [_nvcc(), *NVCC_FLAGS, "-I", str(CSRC), "-o", str(tmp)] + [str(CSRC / s) for s in srcs]
     env = dict(os.environ)
     env.setdefault("TMPDIR", tempfile.gettempdir())
     proc = subprocess.run(cmd, stdout=subprocess.PIPE, stderr=subprocess.STDOUT, text=True, env=env)

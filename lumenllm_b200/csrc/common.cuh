@@ -43,35 +43,19 @@ __host__ __device__ __forceinline__ int tile_offset(int layout, int r, int e, in
 // nothing, and reads of weights, may come first), and then lets the next kernel in the stream
 // start its own set-up early with pdl_trigger(). Launched through lumen_launch with the
 // attribute set, kernels overlap their set-up and first weight loads with the tail of the
-// kernel before; launched without it, both instructions do nothing. It is on by default
+// kernel before; launched without it, both instructions do nothing. It is on
 // (4.11 ms against 4.32 ms a decode step at batch 8 of the 8B shape; the weight-streaming
-// products gain most, 36.6 -> 33.4 us for the gate/up product); LUMEN_PDL=0 turns it off,
-// a comma list of module names (LUMEN_PDL=gemm_tc,core) turns it on for those alone.
+// products gain most, 36.6 -> 33.4 us for the gate/up product); lumen_set_pdl(0) turns it off for
+// the module it is called in, which the kernel micro-benchmarks do on request.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
 #ifdef __CUDACC__
-#include <cstdlib>
 #include <utility>
-#include <cstring>
-#ifndef LUMEN_MODULE
-#define LUMEN_MODULE "?"
-#endif
-static inline bool lumen_pdl_enabled() {
-    static int on = -1;
-    if (on < 0) {
-        const char* e = std::getenv("LUMEN_PDL");
-        on = 1;
-        if (e && e[0] == '0' && e[1] == 0) on = 0;
-        else if (e && !(e[0] == '1' && e[1] == 0) && e[0] != 0) {
-            on = 0;
-            const size_t n = std::strlen(LUMEN_MODULE);
-            for (const char* p = e; (p = std::strstr(p, LUMEN_MODULE)) != nullptr; p += n)
-                if ((p == e || p[-1] == ',') && (p[n] == 0 || p[n] == ',')) { on = 1; break; }
-        }
-    }
-    return on == 1;
-}
+static int g_lumen_pdl = 1;
+static inline bool lumen_pdl_enabled() { return g_lumen_pdl != 0; }
+// Measurement switch of this module (every module is one translation unit and has its own).
+LUMEN_API void lumen_set_pdl(int on) { g_lumen_pdl = on ? 1 : 0; }
 template <typename... KArgs, typename... Args>
 static inline cudaError_t lumen_launch(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem,
                                        cudaStream_t stream, Args&&... args) {

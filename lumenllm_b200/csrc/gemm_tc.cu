@@ -930,6 +930,16 @@ static int sm_count() {
 // 56 us for 4,096 x 12,288. Beyond that the activations fill 128-row tiles of their own.
 static bool tc_swapped(int M, int epi) { return M <= 128 || (M <= 256 && epi == TC_EPI_F32); }
 
+// Measurement switches (the kernel micro-benchmarks set them on request; the defaults are the
+// product): prompt-sized products on the single-SM kernel only, and a fixed tile width for it.
+static int g_tc_two_sm = 1, g_tc_forced_bn = 0;
+LUMEN_API int lumen_gemm_tc_tune(int two_sm, int bn) {
+    if (bn != 0 && (bn < 16 || bn > 256 || bn % 16)) return LUMEN_ERR_BAD_ARGUMENT;
+    g_tc_two_sm = two_sm ? 1 : 0;
+    g_tc_forced_bn = bn;
+    return 0;
+}
+
 static bool tc_two_sm(int M, int N);
 static void tc_plain_plan(int M, int N, int K, int epi, int* bn, int* splits);
 
@@ -991,10 +1001,8 @@ static void tc_plain_plan(int M, int N, int K, int epi, int* bn, int* splits) {
     long narrow_cost;
     *bn = tc_pick_bn(M, N, &narrow_cost);
     *splits = 1;
-    const char* forced = std::getenv("LUMEN_TC_BN");
-    if (forced && forced[0]) {
-        const int v = std::atoi(forced);
-        if (v >= 16 && v <= 256 && v % 16 == 0) *bn = v;
+    if (g_tc_forced_bn) {
+        *bn = g_tc_forced_bn;
         return;
     }
     if (epi != TC_EPI_F32) return;
@@ -1084,8 +1092,7 @@ static int tc2_launch(const CUtensorMap& ma, const CUtensorMap& mb, const CUtens
 // Whether the two-SM kernel takes a prompt-sized product: at least one full wave of 256 x 256
 // tiles for the 74 pairs (fewer tiles are spread better by the single-SM kernel's narrow tiles).
 static bool tc_two_sm(int M, int N) {
-    const char* e = std::getenv("LUMEN_TC_TWO_SM");
-    if (e && e[0] == '0') return false;
+    if (!g_tc_two_sm) return false;
     const long items = (long)((M + 255) / 256) * ((N + 255) / 256);
     return items >= 74;
 }

@@ -7,7 +7,8 @@ prefill/batch/mod.rs:26-63), for B sequences that bring N tokens together:
 
   tokens[N], rope_pos[N] (position used for the rotation), cache_pos[N] (index
   of the token in its sequence's cache), tok_seq[N] (which of the B sequences),
-  seq_slot[B], seq_start[B] (cached length before the step), seq_qlen[B],
+  seq_slot[B] (the state store's spare row for padding sequences), seq_start[B]
+  (cached length before the step), seq_qlen[B],
   cu_q[B+1], want_rows[W] (rows whose logits are wanted), and per cache group a
   page table [B, pages].
 """
@@ -25,10 +26,13 @@ from ..cache.kv import pages_for
 @dataclass
 class StepEntry:
     """One sequence of a step: its slot, its next tokens, and the places among these
-    tokens whose logits are wanted."""
+    tokens whose logits are wanted. `positions`, when given (one per token), are what the
+    position encoding sees (`rope_pos`) instead of the tokens' indices in the cache; where
+    a token's key is stored and which keys it sees still follow the cache index."""
     slot: int
     tokens: Sequence[int]
     want: Sequence[int] = ()
+    positions: Optional[Sequence[int]] = None
 
 
 def _pad4(n: int) -> int:
@@ -93,8 +97,9 @@ class EntryView:
         return self.ctx.cache.groups[self.ctx.cache.group_of[self.cache_entry]].layout
 
     def state(self):
-        """Per-sequence state of fixed size: [max_slots, *shape]; row seq_slot[b] belongs
-        to sequence b. None if the mixer declared none."""
+        """Per-sequence state of fixed size: [max_slots + 1, *shape]; row seq_slot[b] belongs
+        to sequence b (the last row to every padding sequence). None if the mixer declared
+        none."""
         return self.ctx.cache.state.of(self.entry)
 
 
@@ -128,7 +133,8 @@ def pack_step(cache, entries, pad_to: int = 0, table_width: int = 0, want_paddin
     B = max(B_real, pad_to)
     q_lens = [len(e.tokens) for e in entries] + [1] * (B - B_real)
     starts_all = starts + [0] * (B - B_real)
-    slots = [e.slot for e in entries] + [-1] * (B - B_real)
+    # padding sequences point at the state store's spare row, as their writes go to page 0
+    slots = [e.slot for e in entries] + [cache.state.pad_row] * (B - B_real)
     N = sum(q_lens)
     W = sum(len(e.want) for e in entries) + ((B - B_real) if want_padding else 0)
     n_groups = len(cache.groups)
@@ -155,7 +161,8 @@ def pack_step(cache, entries, pad_to: int = 0, table_width: int = 0, want_paddin
             want[w] = n
             w += 1
         pos = np.arange(starts_all[b], starts_all[b] + q, dtype=np.int32)
-        rpos[n:n + q] = pos
+        given = entries[b].positions if b < B_real else None
+        rpos[n:n + q] = pos if given is None else np.asarray(given, dtype=np.int64)
         cpos[n:n + q] = pos
         tseq[n:n + q] = b
         cu[b] = n

@@ -20,6 +20,7 @@ from typing import Dict, List, Sequence, Tuple
 import numpy as np
 import torch
 
+from ..cache.kv import pages_for
 from ..ops import kernels as K
 from .context import StepEntry, StepLayout, context_on, pack_step, upload
 
@@ -71,7 +72,13 @@ class DecodeGraphs:
         q_lens, starts, slots, n_real = lists
         ctx = context_on(meta, lay, q_lens, starts, slots, n_real, eng.cache, eng.runtime)
         ctx.extras["captured"] = True
-        upload(host, meta)
+        # The step is run once before it is captured (library workspaces, kernel attributes).
+        # That run sees padding sequences only, so it changes no live sequence's cache or state;
+        # the capture itself runs nothing, and the first replay is the step's one execution.
+        pad_host, pad_lay = pack_step(eng.cache, [], pad_to=Bb, table_width=lay.width,
+                                      want_padding=True)[:2]
+        assert pad_lay.total == lay.total and pad_lay.offs == lay.offs
+        upload(pad_host, meta)
 
         def body():
             logits = eng.model.forward(ctx)
@@ -115,8 +122,8 @@ class DecodeGraphs:
         Bb = _bucket(n)
         se = [StepEntry(s, t, [0]) for s, t in entries]
         need = max(eng.cache.length(e.slot) + 1 for e in se)
-        Wb = min(_pow2(max(1, (need + 63) // 64)), max(eng.cache.max_pages_per_seq, 1))
-        Wb = max(Wb, (need + 63) // 64, min(self.min_width, eng.cache.max_pages_per_seq))
+        Wb = min(_pow2(max(1, pages_for(need))), max(eng.cache.max_pages_per_seq, 1))
+        Wb = max(Wb, pages_for(need), min(self.min_width, eng.cache.max_pages_per_seq))
         greedy = all(c.greedy for c in configs)
         key = (Bb, Wb, greedy)
         host, lay, q_lens, starts, slots, n_real = pack_step(eng.cache, se, pad_to=Bb, table_width=Wb,

@@ -12,6 +12,7 @@ crates/aegisllm-cuda/src/executor/prefill/batch/builder.rs:15-36,441-469.
 """
 from __future__ import annotations
 
+import warnings
 from dataclasses import dataclass, field
 from pathlib import Path
 from typing import Dict, List, Optional, Sequence
@@ -22,9 +23,11 @@ import torch
 from ..cache.kv import PAGE, KVCache, pages_for
 from ..cache.slots import CacheError, CacheFull
 from ..config import ConfigError, ModelSpec, load_config
+from ..ops import kernels as K
+from ..ops.native import KernelError
 from ..parts.base import Runtime
 from .context import StepContext, StepEntry, build_context
-from .model import DecoderModel, expected_tensors
+from .model import DecoderModel, expected_tensors, tensor_fallbacks
 
 _DTYPES = {"bfloat16": torch.bfloat16, "float32": torch.float32,
            torch.bfloat16: torch.bfloat16, torch.float32: torch.float32}
@@ -83,14 +86,21 @@ class Engine:
     # ------------------------------------------------------------ construction
     @classmethod
     def from_folder(cls, folder, dtype="bfloat16", max_tokens=8192, max_slots=None, device=None,
-                    **kw):
-        """A folder with config.json and model.safetensors; config.json chooses the model."""
+                    strict_weights: bool = True, **kw):
+        """A folder with config.json and model.safetensors; config.json chooses the model.
+        With strict_weights=False tensors that no part reads are warned about, not refused."""
         from ..weights import load_weights
         dev = require_gpu(device)
         config = load_config(folder)
         spec = config.model_spec()
-        exp = {n: shape for n, (shape, _) in expected_tensors(spec).items()}
-        weights = load_weights(folder, exp, dev)
+        tensors = expected_tensors(spec)
+        weights = load_weights(folder, {n: shape for n, (shape, _) in tensors.items()}, dev,
+                               optional=[n for n, (_, kind) in tensors.items() if kind == "optional"],
+                               fallbacks=tensor_fallbacks(spec), strict=strict_weights)
+        for name, other in weights.stood_in.items():
+            warnings.warn(f"{folder}: no tensor '{name}' is stored; '{other}' stands in for it")
+        for name in weights.unexpected:
+            warnings.warn(f"{folder}: tensor '{name}' is stored but no part of the model reads it")
         return cls(spec, weights, dtype, max_tokens, max_slots, dev.index, config=config, **kw)
 
     @classmethod
@@ -135,6 +145,10 @@ class Engine:
                 if not 0 <= int(t) < V:
                     raise StepError(f"slot {e.slot}: token id {t} is outside the vocabulary "
                                     f"of {V}")
+            if e.positions is not None and (len(e.positions) != len(e.tokens)
+                                            or any(int(x) < 0 for x in e.positions)):
+                raise StepError(f"slot {e.slot}: positions must be one non-negative number "
+                                "for each token")
             for w in e.want:
                 if not 0 <= int(w) < len(e.tokens):
                     raise StepError(f"slot {e.slot}: wanted place {w} is not among the "
@@ -205,7 +219,8 @@ class Engine:
                     for gi in rows[ei][w]:
                         wl.append(w - off)
                         origin.append(gi)
-                cur.append(StepEntry(e.slot, toks[off:off + n], wl))
+                cur.append(StepEntry(e.slot, toks[off:off + n], wl,
+                                     None if e.positions is None else list(e.positions)[off:off + n]))
                 off += n
                 room -= n
                 if off < len(toks):   # the rest of this sequence needs a later pass
@@ -216,10 +231,18 @@ class Engine:
         return parts, origin
 
     # ------------------------------------------------------------ generation
+    def check_kernels(self) -> None:
+        """Raises KernelError if a kernel of an earlier step gave up on one of its bounded
+        waits (its output is then not to be used); waits for the device. The engine stays
+        usable: the flag and the kernels' shared counters are put back."""
+        K.check_error_flags()
+
     def run(self, entries, configs, uniforms) -> List[int]:
         """Backend face of the generation loop: feeds each (slot, tokens), samples one
         token per sequence from the logits at its last token, returns them on the host."""
-        return self.run_device(entries, configs, uniforms).tolist()
+        toks = self.run_device(entries, configs, uniforms).tolist()
+        self.check_kernels()
+        return toks
 
     def run_device(self, entries, configs, uniforms, tokens_on_device=None) -> torch.Tensor:
         """As `run`, but the sampled tokens stay on the device (int32 [len(entries)])."""
@@ -253,18 +276,26 @@ class Engine:
         # pinned buffers in turn leave room to spare
         ring = self.__dict__.setdefault("_host_ring", [])
         if not ring:
-            ring.extend(torch.empty((max(self.cache.max_slots, 1),), dtype=torch.int32).pin_memory()
+            # the tokens, and behind them the kernels' error flag as it stands after the step
+            ring.extend(torch.zeros((max(self.cache.max_slots, 1) + 1,), dtype=torch.int32).pin_memory()
                         for _ in range(4))
         self._launched = getattr(self, "_launched", 0) + 1
         host = ring[self._launched % len(ring)]
         host[:n].copy_(dev[:n], non_blocking=True)
+        host[-1:].copy_(K.error_flag(self.device), non_blocking=True)
         done = torch.cuda.Event()
         done.record()
         return _InFlight(dev[:n], host, done, n)
 
     def collect(self, handle: "_InFlight") -> List[int]:
-        """The sampled tokens of a launched step, on the host."""
+        """The sampled tokens of a launched step, on the host. Raises KernelError instead if
+        a kernel of that step (or of one before it) gave up on a bounded wait."""
         handle.done.synchronize()
+        if int(handle.host[-1]) != 0:
+            torch.cuda.synchronize(self.device)      # the step run ahead is abandoned with it
+            K.recover(self.device)
+            raise KernelError(f"a kernel on {self.device} gave up waiting for its own copies; "
+                              "the step's tokens are not valid")
         return handle.host[:handle.n].tolist()
 
     def generate(self, requests, eos_token_ids=None, max_batch: int = 64, on_token=None):

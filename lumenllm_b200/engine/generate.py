@@ -37,6 +37,7 @@ import time
 from dataclasses import dataclass, field
 from typing import Callable, List, Optional, Sequence
 
+from ..cache.kv import PAGE
 from ..sampling import SamplingConfig, fresh_seed, uniform
 
 
@@ -64,14 +65,14 @@ class GenerationError(ValueError):
     pass
 
 
-def tokens_held(req: GenerateRequest, page: int = 64) -> int:
+def tokens_held(req: GenerateRequest, page: int = PAGE) -> int:
     """Most cache a request can come to hold: the last allowed token is never fed back."""
     n = len(req.prompt_tokens) + max(0, req.max_tokens - 1)
     return (n + page - 1) // page * page
 
 
 def plan_batches(requests: Sequence[GenerateRequest], max_batch: int, token_budget: int,
-                 page: int = 64) -> List[List[int]]:
+                 page: int = PAGE) -> List[List[int]]:
     """Cuts the requests, in their order, into batches that fit the slots and the cache."""
     if max_batch <= 0:
         raise GenerationError("max_batch must be positive")

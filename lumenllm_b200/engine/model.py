@@ -15,7 +15,8 @@ from .context import EntryView, StepContext
 
 
 def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
-    """Every tensor the model reads, by name, with its shape and kind."""
+    """Every tensor the model reads, by name, with its shape and kind: "matrix", "norm", or
+    "optional" (a matrix that is read if the file stores it and not missed if it does not)."""
     t = {}
     t.update(part_tensors("embedding", spec.embedding))
     for layer in spec.layers:
@@ -23,6 +24,12 @@ def expected_tensors(spec: ModelSpec) -> Dict[str, Tuple[Tuple[int, ...], str]]:
     t.update(part_tensors("norm", spec.final_norm))
     t.update(part_tensors("head", spec.head))
     return t
+
+
+def tensor_fallbacks(spec: ModelSpec) -> Dict[str, str]:
+    """{tensor: the stored tensor that may stand in when it is absent}, as parts declare."""
+    f = getattr(part_class("head", spec.head.kind), "fallbacks", None)
+    return dict(f(spec.head)) if f else {}
 
 
 class DecoderModel:

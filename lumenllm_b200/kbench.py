@@ -18,6 +18,7 @@ from __future__ import annotations
 
 import argparse
 import math
+from ctypes import c_int
 
 import torch
 
@@ -47,10 +48,10 @@ def _time(fns, reps):
 
 
 def _paged(B, length, nkv, d, dev):
-    pages = (length + 63) // 64
+    pages = (length + K.PAGE - 1) // K.PAGE
     n_pages = B * pages + 1
-    kc = torch.randn(n_pages, nkv, 64, d, device=dev).to(torch.bfloat16)
-    vc = torch.randn(n_pages, nkv, 64, d, device=dev).to(torch.bfloat16)
+    kc = torch.randn(n_pages, nkv, K.PAGE, d, device=dev).to(torch.bfloat16)
+    vc = torch.randn(n_pages, nkv, K.PAGE, d, device=dev).to(torch.bfloat16)
     table = (torch.arange(B * pages, device=dev, dtype=torch.int32) + 1).view(B, pages)
     return kc, vc, table
 
@@ -76,7 +77,24 @@ def main(argv=None):
     ap.add_argument("--head-dim", type=int, default=128)
     ap.add_argument("--copies", type=int, default=8)
     ap.add_argument("--reps", type=int, default=5)
+    ap.add_argument("--no-pdl", action="store_true",
+                    help="launch without programmatic dependent launch")
+    ap.add_argument("--single-sm", action="store_true",
+                    help="gemm_tc: keep prompt-sized products on the single-SM kernel")
+    ap.add_argument("--bn", type=int, default=0, help="gemm_tc: fix the single-SM kernel's tile width")
+    ap.add_argument("--seg-pages", type=int, default=0,
+                    help="attn_decode: pages a block walks (default: the product's rule)")
     a = ap.parse_args(argv)
+    from .ops import native
+    if a.no_pdl:
+        native.preload(["core", "gemm_tc", "attn_decode", "attn_prefill_tc", "attn_prefill", "sample"])
+        native.set_dependent_launch(False)
+    if a.single_sm or a.bn:
+        native.check(native.int_fn("gemm_tc", "lumen_gemm_tc_tune", [c_int, c_int])(0 if a.single_sm else 1, a.bn),
+                     "gemm_tc_tune")
+        native.launches -= 1
+    if a.seg_pages:
+        K.DECODE_SEG_PAGES = a.seg_pages
     dev = torch.device("cuda", 0)
     torch.manual_seed(0)
     bf = torch.bfloat16

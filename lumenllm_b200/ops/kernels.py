@@ -11,6 +11,7 @@ from ctypes import c_float, c_int, c_longlong, c_void_p
 
 import torch
 
+from ..csrc.build import page_size as _page_size
 from .native import KernelError, check, fn, int_fn, library, ptr, require, stream_ptr
 
 P = c_void_p
@@ -18,7 +19,7 @@ F32 = torch.float32
 BF16 = torch.bfloat16
 I32 = torch.int32
 
-PAGE = 64  # tokens per cache page; equals LUMEN_PAGE in csrc/common.cuh
+PAGE = _page_size()   # tokens per cache page: LUMEN_PAGE of csrc/common.cuh
 LAYOUT_LINEAR, LAYOUT_SW128 = 0, 1   # tile layouts of the cache, as in csrc/common.cuh
 
 
@@ -179,8 +180,8 @@ def gemm_tc_qkv(x, w, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, tok_se
     require(block_table, I32, "block_table")
     require(kcache, BF16, "kcache")
     require(vcache, BF16, "vcache")
-    if kcache.shape[1:] != (nkv, 64, 128) or vcache.shape != kcache.shape:
-        raise KernelError("gemm_tc_qkv: caches must be [pages, nkv, 64, 128]")
+    if kcache.shape[1:] != (nkv, PAGE, 128) or vcache.shape != kcache.shape:
+        raise KernelError(f"gemm_tc_qkv: caches must be [pages, nkv, {PAGE}, 128]")
     q_out = torch.empty((M, nq, 128), dtype=BF16, device=x.device)
     f = fn("gemm_tc", "lumen_gemm_tc_qkv",
            [P, P, c_int, c_int, c_int, P, P, P, P, P, c_float, P, c_int, P, P, P, c_int, c_int, c_int, P, P])
@@ -313,8 +314,18 @@ def check_error_flags() -> None:
     """Raises if any kernel gave up on a wait since the last check (synchronises)."""
     for dev, t in _err_flags.items():
         if int(t.item()) != 0:
-            t.zero_()
+            recover(dev)
             raise KernelError(f"a kernel on cuda:{dev} gave up waiting for its own copies")
+
+
+def recover(device) -> None:
+    """After a kernel gave up: the flag back to zero, and the counters that the decode
+    attention's blocks leave at zero only when all of them arrive."""
+    key = torch.device("cuda", device).index if isinstance(device, int) else torch.device(device).index
+    for table in (_err_flags, _counters):
+        t = table.get(key)
+        if t is not None:
+            t.zero_()
 
 
 _COUNTERS = 1 << 16
@@ -332,14 +343,11 @@ def _decode_counters(device) -> torch.Tensor:
 
 
 DECODE_MAX_SEGS = 32
-
-
-def decode_segment_pages(B, nkv) -> int:
-    """Pages a decode-attention block walks (unless the sequence is longer than 32 segments):
-    8 when the batch brings blocks enough, fewer (down to 2) for a small batch, so that a short
-    batch is spread over more SMs. A function of the batch and the kv heads only, never of the page
-    table's width, so a wider (padded) table does not change a result."""
-    return max(2, min(8, (B * nkv) // 8))
+# Pages a decode-attention block walks (unless the sequence is longer than 32 segments of them).
+# One number for every batch: how a sequence's keys are cut, and so the order in which its
+# partial results are merged, depends on the sequence alone, never on who else is in the batch
+# or on the page table's width.
+DECODE_SEG_PAGES = 4
 
 
 def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
@@ -355,7 +363,7 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     if seq_pos.numel() < B or block_table.shape[0] < B:
         raise KernelError("attn_decode: metadata shorter than the batch")
     width = block_table.shape[1]
-    seg_pages = decode_segment_pages(B, nkv)
+    seg_pages = DECODE_SEG_PAGES
     max_segs = min(-(-width // seg_pages), DECODE_MAX_SEGS)
     out = torch.empty_like(q)
     part_o = torch.empty((B, nq, max_segs, d), dtype=F32, device=q.device)

@@ -47,10 +47,22 @@ def preload(modules) -> None:
         library(m)
 
 
+def set_dependent_launch(on: bool, modules=None) -> None:
+    """Measurement switch: programmatic dependent launch on or off for the given modules (all
+    that are loaded when none are named). The product never calls this; it is on."""
+    for m in (list(_libs) if modules is None else modules):
+        f = library(m).lumen_set_pdl
+        f.restype, f.argtypes = None, [ctypes.c_int]
+        f(1 if on else 0)
+
+
 _fn_cache: dict = {}
 
 
-def fn(module: str, name: str, argtypes):
+_probe = None
+
+
+def _raw_fn(module: str, name: str, argtypes):
     key = (module, name)
     f = _fn_cache.get(key)
     if f is None:
@@ -59,6 +71,30 @@ def fn(module: str, name: str, argtypes):
         f.argtypes = list(argtypes)
         _fn_cache[key] = f
     return f
+
+
+def fn(module: str, name: str, argtypes):
+    """The C entry point `name` of a module (one that launches kernels)."""
+    f = _raw_fn(module, name, argtypes)
+    return f if _probe is None else _bracketed(name, f)
+
+
+def instrument(probe) -> None:
+    """Measurement hook: with `probe(name, args) -> (label, start event, end event)` every
+    kernel entry point called from now on records the two events around its launch; None
+    switches it off again. The product never sets it."""
+    global _probe
+    _probe = probe
+
+
+def _bracketed(name, f):
+    def call(*args):
+        _, e0, e1 = _probe(name, args)
+        e0.record()
+        rc = f(*args)
+        e1.record()
+        return rc
+    return call
 
 
 launches = 0   # kernels of this library launched (or recorded into a graph) so far
@@ -93,7 +129,7 @@ def stream_ptr() -> int:
 
 def int_fn(module: str, name: str, argtypes):
     """A C function of a module that returns a plain number (no launch, no error code)."""
-    return fn(module, name, argtypes)
+    return _raw_fn(module, name, argtypes)
 
 
 def ptr(t):

@@ -34,15 +34,27 @@ class TokenEmbedding:
 
 @register_part("head", "linear_head")
 class LinearHead:
+    """`tied_to` names the embedding table when config.json ties the head to it. Which matrix
+    is used follows the reference, by presence (executor/full.rs:171-181): the head's own
+    tensor when the file stores one, else the table named by `tied_to` or `falls_back_to`.
+    So a tied checkpoint that also stores a head, and an untied one that stores none, both
+    load; the loader reports the second case in its `stood_in`."""
+
     @classmethod
     def tensors(cls, spec):
-        if spec.params.get("tied_to"):
-            return {}
-        return {f"{spec.prefix}.weight": ((int(need(spec.params, "vocab_size", "head")),
-                                           int(need(spec.params, "hidden_size", "head"))), "matrix")}
+        shape = (int(need(spec.params, "vocab_size", "head")), int(need(spec.params, "hidden_size", "head")))
+        return {f"{spec.prefix}.weight": (shape, "optional" if spec.params.get("tied_to") else "matrix")}
+
+    @classmethod
+    def fallbacks(cls, spec):
+        other = spec.params.get("falls_back_to")
+        return {f"{spec.prefix}.weight": other} if other and not spec.params.get("tied_to") else {}
 
     def __init__(self, spec, weights, runtime):
-        name = spec.params.get("tied_to") or f"{spec.prefix}.weight"
+        own = f"{spec.prefix}.weight"
+        name = own if own in weights else spec.params.get("tied_to")
+        if name is None or name not in weights:
+            raise KeyError(f"the output head needs '{own}'")
         self.proj = Linear(weights[name], runtime)
 
     def forward(self, y):

@@ -7,6 +7,16 @@ files hold and raises ONE WeightError that lists every missing tensor, every
 unexpected tensor and every wrong shape; then it copies the tensors to the
 device. bfloat16 stays bfloat16, a tensor stored in 32-bit float stays so,
 float16 is widened to float32 (exact), integer tables become int32.
+
+Three things soften the comparison, each named by the caller. `optional` tensors
+are loaded when stored and not missed when absent. `fallbacks` {name: other}
+let a missing tensor stand for another one that is stored: the reference takes
+the output head from `lm_head.weight` when the file has it and from the
+embedding when not, whatever config.json says
+(crates/aegisllm-cuda/src/executor/full.rs:171-181). Names in IGNORED_SUFFIXES
+(tables that older exporters store and no model reads) are never unexpected.
+With strict=False other unexpected tensors are reported in the result's
+`unexpected` list instead of raising.
 """
 from __future__ import annotations
 
@@ -65,16 +75,36 @@ def _kept_dtype(stored: str):
     return None
 
 
+IGNORED_SUFFIXES = ("rotary_emb.inv_freq",)
+
+
+class LoadedWeights(dict):
+    """name -> tensor, with what the comparison let pass: `unexpected` (stored, read by
+    nobody; only with strict=False) and `stood_in` {missing name: the stored tensor used}."""
+    unexpected: list = []
+    stood_in: dict = {}
+
+
 def check_against(expected: Dict[str, Tuple[int, ...]], infos: Dict[str, TensorInfo],
-                  where: str = "checkpoint") -> None:
-    missing = sorted(n for n in expected if n not in infos)
-    unexpected = sorted(n for n in infos if n not in expected)
+                  where: str = "checkpoint", optional=(), fallbacks=None, strict: bool = True):
+    """Raises the one WeightError, or returns (unexpected names, {missing: stand-in})."""
+    optional, fallbacks = set(optional), dict(fallbacks or {})
+    stood_in = {n: fallbacks[n] for n in expected
+                if n not in infos and n in fallbacks and fallbacks[n] in infos
+                and tuple(infos[fallbacks[n]].shape) == tuple(expected[n])}
+    missing = sorted(n for n in expected if n not in infos and n not in optional
+                     and n not in stood_in)
+    unexpected = sorted(n for n in infos if n not in expected and not n.endswith(IGNORED_SUFFIXES))
     wrong = [(n, tuple(expected[n]), infos[n].shape) for n in sorted(expected)
              if n in infos and tuple(infos[n].shape) != tuple(expected[n])]
     bad_dtype = [(n, infos[n].dtype) for n in sorted(expected)
                  if n in infos and _kept_dtype(infos[n].dtype) is None]
+    if not strict:
+        passed, unexpected = unexpected, []
+    else:
+        passed = []
     if not (missing or unexpected or wrong or bad_dtype):
-        return
+        return passed, stood_in
     lines = [f"{where} does not match the model:"]
     if missing:
         lines.append(f"  missing tensors ({len(missing)}):")
@@ -91,13 +121,18 @@ def check_against(expected: Dict[str, Tuple[int, ...]], infos: Dict[str, TensorI
     raise WeightError("\n".join(lines), missing, unexpected, wrong, bad_dtype)
 
 
-def load_weights(folder, expected: Dict[str, Tuple[int, ...]], device) -> Dict[str, torch.Tensor]:
+def load_weights(folder, expected: Dict[str, Tuple[int, ...]], device, optional=(),
+                 fallbacks=None, strict: bool = True) -> LoadedWeights:
     infos = open_checkpoint(folder)
-    check_against(expected, infos, where=str(folder))
+    passed, stood_in = check_against(expected, infos, where=str(folder), optional=optional,
+                                     fallbacks=fallbacks, strict=strict)
     files: Dict[Path, MappedFile] = {}
-    out: Dict[str, torch.Tensor] = {}
+    out = LoadedWeights()
+    out.unexpected, out.stood_in = list(passed), dict(stood_in)
     try:
         for name in expected:
+            if name not in infos:
+                continue                  # optional and absent, or stood in for below
             info = infos[name]
             mf = files.get(info.file)
             if mf is None:
@@ -112,4 +147,6 @@ def load_weights(folder, expected: Dict[str, Tuple[int, ...]], device) -> Dict[s
     finally:
         for mf in files.values():
             mf.close()
+    for name, other in stood_in.items():
+        out[name] = out[other]
     return out

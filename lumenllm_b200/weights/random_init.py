@@ -37,9 +37,10 @@ def random_tensor(name: str, shape, kind: str, seed: int, std: float, norm_jitte
 
 def random_weights(expected: Dict[str, Tuple[Tuple[int, ...], str]], seed: int, std=0.02,
                    norm_jitter=0.0, dtype=torch.bfloat16, device="cpu") -> Dict[str, torch.Tensor]:
-    """expected: name -> (shape, kind) with kind "matrix" or "norm"."""
+    """expected: name -> (shape, kind) with kind "matrix" or "norm"; "optional" tensors are
+    not made."""
     return {n: random_tensor(n, shape, kind, seed, std, norm_jitter, dtype, device)
-            for n, (shape, kind) in expected.items()}
+            for n, (shape, kind) in expected.items() if kind != "optional"}
 
 
 def write_random_model(config, folder, seed: int = 0, std: float = 0.02, norm_jitter: float = 0.0,

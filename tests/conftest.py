@@ -78,8 +78,95 @@ def seeded_tokens(vocab, lengths, seed):
 
 
 def tolerance(dtype, ref):
-    """float32: float32 rounding over a few hundred terms. bfloat16: activations are
-    rounded to 8 bits of mantissa about six times a layer; the bound is 3 % of the
-    logits' scale."""
+    """Bound on |engine - plain float32| for logits. float32: float32 rounding over a few
+    hundred terms (worst seen on a B200: 6e-6 of the logits' scale). bfloat16: what rounding
+    the activations to 8 bits of mantissa at nine places a layer does to a tiny model's
+    logits; the worst seen is 1.0e-2 of the scale, and the plain implementation with the same
+    roundings alone differs from the plain float32 one by up to 0.8e-2 on these models."""
     scale = max(1.0, float(ref.abs().max()))
-    return 2e-5 * scale if dtype == "float32" else 3e-2 * scale
+    return 2e-5 * scale if dtype == "float32" else 2e-2 * scale
+
+
+# |engine bfloat16 - plain implementation with the same roundings|, as a fraction of the
+# logits' scale (max |logit|, at least 1); worst seen 1.0e-2. It is not far below the bound
+# above: at widths of 64 to 128 a single 16-bit rounding that falls the other way (because
+# a float32 sum was taken in another order) moves every output of the next product enough to
+# turn some of ITS roundings, so the two computations drift apart as two roundings of the
+# same numbers would. Stage by stage (tests of the parts and kernels) they agree to a few
+# units in the last place of bfloat16.
+BF16_VS_ROUNDED = 1.5e-2
+
+_observed = {}
+
+
+def record_error(kind, dtype, err, scale, what=""):
+    model = what.split(" ")[0] if what.split(" ")[0] in TINY else "-"
+    k = (f"{kind} [{model}]", dtype)
+    worst = _observed.get(k, (0.0, 1.0, 0))
+    _observed[k] = (max(worst[0], err / scale), scale if err / scale > worst[0] else worst[1], worst[2] + 1)
+
+
+def pytest_terminal_summary(terminalreporter):
+    if not _observed:
+        return
+    terminalreporter.write_line("worst observed |engine - plain| / max(1, max|logit|):")
+    for (kind, dtype), (rel, scale, n) in sorted(_observed.items()):
+        terminalreporter.write_line(f"  {dtype:9s} {kind:34s} {rel:.3e}  (scale {scale:.2f}, {n} comparisons)")
+    path = os.environ.get("LUMEN_TEST_ERRORS")
+    if path:
+        import json
+        with open(path, "w") as f:
+            json.dump({f"{d}:{k}": v[0] for (k, d), v in _observed.items()}, f, indent=1)
+
+
+class Ref:
+    """Plain logits of a sequence twice: all float32, and with activations rounded to
+    bfloat16 where the serving path rounds them. Indexing takes the same rows of both."""
+
+    def __init__(self, f32, b16):
+        self.f32, self.b16 = f32, b16
+
+    def __getitem__(self, idx):
+        return Ref(self.f32[idx], self.b16[idx])
+
+    @property
+    def shape(self):
+        return self.f32.shape
+
+    @staticmethod
+    def cat(refs):
+        return Ref(torch.cat([r.f32 for r in refs]), torch.cat([r.b16 for r in refs]))
+
+    @staticmethod
+    def stack(refs):
+        return Ref(torch.stack([r.f32 for r in refs]), torch.stack([r.b16 for r in refs]))
+
+
+def plain_ref(cfg, w, tokens, **kw):
+    import plain_qwen3 as P
+    return Ref(P.forward_logits(cfg, w, tokens, **kw),
+               P.forward_logits(cfg, w, tokens, round_to=torch.bfloat16, **kw))
+
+
+def check(got, ref, dtype, what):
+    """Engine logits against the plain implementation: float32 against the float32 plain
+    logits; bfloat16 against those (wide bound) and, tightly, against the plain logits made
+    with the same roundings."""
+    r32 = ref.f32 if isinstance(ref, Ref) else ref
+    assert got.shape == r32.shape, what
+    assert torch.isfinite(got).all(), what
+
+    def one(r, tol, kind):
+        scale = max(1.0, float(r.abs().max()))
+        err = float((got - r).abs().max())
+        record_error(kind, dtype, err, scale, what)
+        if err > tol * scale:
+            bad = int((got - r).abs().max(dim=1).values.argmax())
+            raise AssertionError(f"{what}: max abs error {err:.3e} > {tol * scale:.3e} ({kind}); "
+                                 f"worst position {bad} of {got.shape[0]}")
+    if dtype == "float32":
+        one(r32, 2e-5, "vs plain float32")
+    else:
+        one(r32, 2e-2, "vs plain float32")
+        if isinstance(ref, Ref):
+            one(ref.b16, BF16_VS_ROUNDED, "vs plain with bf16 roundings")

@@ -94,12 +94,29 @@ def apply_rope(x, positions, theta, rotary_dim=None):
     return out
 
 
-def causal_attention(q, k, v, window=0, scale=None):
+def _same(t):
+    return t
+
+
+def rounded_to(dtype):
+    """A function that rounds a float32 tensor to `dtype` and widens it again: the places
+    where the serving path keeps activations in 16 bits (the inputs of matrix products, the
+    cache, the softmax weights that multiply the values) are marked with it below. The
+    reference rounds at the same places, to float16: activations of prompt products
+    (crates/aegisllm-cuda/src/cuda/runtime/cublaslt.rs:99-164), the cache
+    (norm_rope_kv.cu:623-651), the weights P of the prompt attention
+    (attention_prefill_dense_wmma.cu:3013-3021)."""
+    return lambda t: t.to(dtype).to(torch.float32)
+
+
+def causal_attention(q, k, v, window=0, scale=None, rnd=_same):
     """Full [T, T] masked softmax. Query head h reads kv head h // (nq / nkv);
     scores scaled by 1/sqrt(d); a query at position p sees keys j <= p, and with
     a window W only those with p - j < W
     (crates/aegisllm-cpu/src/attention.rs:127-236;
-    attention_decode_common.cuh:112-115).
+    attention_decode_common.cuh:112-115). With `rnd` the weights exp(s - max) are rounded
+    before they multiply the values while their sum is taken unrounded, as the reference's
+    prompt kernel does (attention_prefill_dense_wmma.cu:2990-2994,3013-3021).
     q: [T, nq, d], k, v: [T, nkv, d] -> [T, nq, d]."""
     T, nq, d = q.shape
     nkv = k.shape[1]
@@ -115,8 +132,12 @@ def causal_attention(q, k, v, window=0, scale=None):
         kh = h // group
         s = (q[:, h, :] @ k[:, kh, :].T) * scale
         s = s.masked_fill(~visible, float("-inf"))
-        p = torch.softmax(s, dim=-1)
-        out[:, h, :] = p @ v[:, kh, :]
+        if rnd is _same:
+            p = torch.softmax(s, dim=-1)
+            out[:, h, :] = p @ v[:, kh, :]
+        else:
+            e = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+            out[:, h, :] = (rnd(e) @ v[:, kh, :]) / e.sum(dim=-1, keepdim=True)
     return out
 
 
@@ -144,7 +165,7 @@ def layer_window(cfg, i):
     return 0
 
 
-def attention_block(x, w, prefix, cfg, positions, window):
+def attention_block(x, w, prefix, cfg, positions, window, rnd=_same):
     """norm -> q,k,v -> per-head q/k RMSNorm -> RoPE -> attention -> o_proj
     (crates/aegisllm-cuda/src/executor/attention.rs:139-202,241-250,413-425, with
     the Gemma-only V-norm and q*sqrt(d) of :203-219,262-269 off)."""
@@ -159,40 +180,45 @@ def attention_block(x, w, prefix, cfg, positions, window):
     v = (x @ w[prefix + "self_attn.v_proj.weight"].T).view(T, nkv, d)
     q = rms_norm(q, w[prefix + "self_attn.q_norm.weight"], eps)
     k = rms_norm(k, w[prefix + "self_attn.k_norm.weight"], eps)
-    q = apply_rope(q, positions, theta)
-    k = apply_rope(k, positions, theta)
-    ctx = causal_attention(q, k, v, window=window)
+    q = rnd(apply_rope(q, positions, theta))
+    k = rnd(apply_rope(k, positions, theta))
+    ctx = rnd(causal_attention(q, k, rnd(v), window=window, rnd=rnd))
     return ctx.reshape(T, nq * d) @ w[prefix + "self_attn.o_proj.weight"].T
 
 
-def mlp_block(x, w, prefix):
+def mlp_block(x, w, prefix, rnd=_same):
     """gate, up -> SwiGLU -> down (crates/aegisllm-cuda/src/executor/mlp.rs:271-356)."""
     g = x @ w[prefix + "mlp.gate_proj.weight"].T
     u = x @ w[prefix + "mlp.up_proj.weight"].T
-    return swiglu(g, u) @ w[prefix + "mlp.down_proj.weight"].T
+    return rnd(swiglu(g, u)) @ w[prefix + "mlp.down_proj.weight"].T
 
 
-def decoder_layer(h, w, i, cfg, positions):
+def decoder_layer(h, w, i, cfg, positions, rnd=_same):
     """Pre-norm residual block: r = h + attn(norm1(h)); h' = r + mlp(norm2(r))
     (crates/aegisllm-cuda/src/executor/prefill/layer.rs:476-482,1090,1381-1439)."""
     p = f"model.layers.{i}."
     eps = cfg.get("rms_norm_eps", 1e-5)
-    y = rms_norm(h, w[p + "input_layernorm.weight"], eps)
-    r = h + attention_block(y, w, p, cfg, positions, layer_window(cfg, i))
-    y2 = rms_norm(r, w[p + "post_attention_layernorm.weight"], eps)
-    return r + mlp_block(y2, w, p)
+    y = rnd(rms_norm(h, w[p + "input_layernorm.weight"], eps))
+    r = h + attention_block(y, w, p, cfg, positions, layer_window(cfg, i), rnd)
+    y2 = rnd(rms_norm(r, w[p + "post_attention_layernorm.weight"], eps))
+    return r + mlp_block(y2, w, p, rnd)
 
 
-def forward_logits(cfg, w, tokens):
+def forward_logits(cfg, w, tokens, positions=None, round_to=None):
     """Logits [T, V] at every position of one whole sequence
     (final norm + head: crates/aegisllm-cuda/src/executor/forward.rs:281-298;
-    tied head when lm_head.weight is absent: executor/full.rs:171-181)."""
+    tied head when lm_head.weight is absent: executor/full.rs:171-181). `positions`
+    (default 0, 1, 2, ...) are what the rotation sees; the causal mask follows the order of
+    the tokens (prefill/mod.rs:136-141 keeps the two apart). With `round_to` the activations
+    are rounded where a 16-bit serving path rounds them (see rounded_to); the residual
+    stream, norms, softmax and every sum stay float32."""
     tokens = torch.as_tensor(tokens, dtype=torch.long)
-    positions = torch.arange(tokens.numel())
+    positions = torch.arange(tokens.numel()) if positions is None else torch.as_tensor(positions)
+    rnd = _same if round_to is None else rounded_to(round_to)
     h = embed(tokens, w["model.embed_tokens.weight"])
     for i in range(cfg["num_hidden_layers"]):
-        h = decoder_layer(h, w, i, cfg, positions)
-    y = rms_norm(h, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5))
+        h = decoder_layer(h, w, i, cfg, positions, rnd)
+    y = rnd(rms_norm(h, w["model.norm.weight"], cfg.get("rms_norm_eps", 1e-5)))
     head = w.get("lm_head.weight", w["model.embed_tokens.weight"])
     return y @ head.T
 

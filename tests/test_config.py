@@ -133,3 +133,25 @@ def test_parameters_file(tmp_path):
         ParametersFile.from_dict({"model": {"path": "m", "hidden-layers": {
             "kv-cache": {"type-k": "fp8"}}}})
     assert ParametersFile.from_dict({"model": {"path": "m"}}).sampling.temperature == 0.0
+
+
+def test_eos_ids_are_the_union_of_both_files(tmp_path):
+    """config.json names one id, generation_config.json another (a number or a list in either):
+    generation stops at both; a folder without the second file keeps config.json's."""
+    import json
+    from lumenllm_b200.config import load_config
+    (tmp_path / "config.json").write_text(json.dumps(dict(TINY["B"], eos_token_id=5)))
+    assert load_config(tmp_path).model_spec().eos_token_ids == (5,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": [9, 5], "top_k": 20}))
+    assert load_config(tmp_path).model_spec().eos_token_ids == (5, 9)
+    (tmp_path / "config.json").write_text(json.dumps(dict(TINY["B"])))
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": 7}))
+    assert load_config(tmp_path).model_spec().eos_token_ids == (7,)
+    (tmp_path / "generation_config.json").write_text(json.dumps({"temperature": 0.6}))
+    assert load_config(tmp_path).model_spec().eos_token_ids == ()
+    (tmp_path / "generation_config.json").write_text(json.dumps({"eos_token_id": "x"}))
+    with pytest.raises(ConfigError, match="generation_config.json.*eos_token_id"):
+        load_config(tmp_path)
+    (tmp_path / "generation_config.json").write_text("{not json")
+    with pytest.raises(ConfigError, match="not valid JSON"):
+        load_config(tmp_path)

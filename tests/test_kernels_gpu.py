@@ -275,6 +275,75 @@ def test_attention_decode_kernel(nq, nkv, d, window):
     assert torch.equal(out, out2)
 
 
+def _last_query_attention(q, k, v, window):
+    """The plain attention of the newest token alone (no other query exists in a decode
+    step): weights softmax(q . k_j / sqrt(d)) over the keys j it sees, in float64.
+    q [nq, d]; k, v [T, nkv, d]. Same formulas as plain_qwen3.causal_attention
+    (crates/aegisllm-cpu/src/attention.rs:127-236; attention_decode_common.cuh:112-115)."""
+    T, nkv, d = k.shape
+    nq = q.shape[0]
+    lo = max(0, T - window) if window > 0 else 0
+    out = torch.empty(nq, d, dtype=torch.float64)
+    for h in range(nq):
+        kh = h // (nq // nkv)
+        s = (k[lo:, kh].double() @ q[h].double()) / math.sqrt(d)
+        out[h] = torch.softmax(s, dim=0) @ v[lo:, kh].double()
+    return out.float()
+
+
+@pytest.mark.parametrize("starts,window", [([4199], 0), ([8999], 0), ([8999], 3000),
+                                           ([16999, 8191, 8192, 63, 12345, 4200, 100, 9000], 0),
+                                           ([16999, 8191, 8192, 63, 12345, 4200, 100, 9000], 5000)])
+def test_attention_decode_of_long_sequences(starts, window):
+    """Sequences longer than 32 segments of the split attention (beyond 8,192 keys a block
+    walks more pages than a segment usually has), at the cap and one page past it, with and
+    without a window, alone and in a batch of 8 unequal ones. In every sequence one early
+    key, which only the first segment holds, is made to matter."""
+    from lumenllm_b200.ops import kernels as K
+    nq, nkv, d = 4, 2, 128
+    B = len(starts)
+    g = gen(17)
+    n_pages = sum((s + 64) // 64 for s in starts) + 2
+    kc = torch.zeros(n_pages, nkv, 64, d, dtype=BF16)
+    vc = torch.zeros_like(kc)
+    width = max((s + 64) // 64 for s in starts)
+    table = torch.zeros(B, width, dtype=I32)
+    order = torch.randperm(n_pages - 1, generator=g) + 1
+    at = 0
+    qs, refs = [], []
+    for b, s in enumerate(starts):
+        T = s + 1
+        k = torch.randn(T, nkv, d, generator=g)
+        v = torch.randn(T, nkv, d, generator=g)
+        q = torch.randn(nq, d, generator=g)
+        far = max(0, T - window) + 5 if window else 5            # inside the first page seen
+        if far < T:
+            q[0, :8] = 4.0
+            k[far, 0, :8] = 4.0                               # score +128/sqrt(128) = 11 above the rest
+        k, v, q = k.to(BF16), v.to(BF16), q.to(BF16)
+        np_ = (T + 63) // 64
+        pages = order[at:at + np_]
+        at += np_
+        table[b, :np_] = pages.to(I32)
+        pad = np_ * 64 - T
+        kp = torch.cat([k, torch.zeros(pad, nkv, d, dtype=BF16)]).view(np_, 64, nkv, d).transpose(1, 2)
+        vp = torch.cat([v, torch.zeros(pad, nkv, d, dtype=BF16)]).view(np_, 64, nkv, d).transpose(1, 2)
+        kc[pages] = kp
+        vc[pages] = vp
+        qs.append(q)
+        refs.append(_last_query_attention(q.float(), k.float(), v.float(), window))
+    out = K.attn_decode(dev(torch.stack(qs)), dev(to_sw128(kc)), dev(to_sw128(vc)), dev(table),
+                        dev(torch.tensor(starts, dtype=I32)), window, d ** -0.5).cpu().float()
+    K.check_error_flags()
+    err = (out - torch.stack(refs)).abs().amax(dim=(1, 2))
+    assert float(err.max()) < 2 ** -6, (err.tolist(), starts, window)
+    # the general kernel walks the same cache in its own chunks
+    out_g = K.attn_generic(dev(torch.stack(qs)), dev(to_sw128(kc)), dev(to_sw128(vc)), dev(table),
+                           dev(torch.arange(B, dtype=I32)), dev(torch.tensor(starts, dtype=I32)), window,
+                           d ** -0.5, layout=K.LAYOUT_SW128).cpu().float()
+    assert float((out_g - torch.stack(refs)).abs().max()) < 2 ** -6
+
+
 @pytest.mark.parametrize("tensor_memory", [True, False])
 @pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, 0), (4, 2, 64, 0), (6, 2, 64, 0), (5, 1, 128, 0),
                                             (16, 1, 64, 0), (2, 2, 128, 0), (8, 2, 128, 70), (4, 2, 64, 24)])

@@ -284,6 +284,112 @@ def test_a_toy_mixer_with_state_of_its_own(dtype, tiny_models):
     eng.cache.check()
 
 
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_a_toy_mixer_with_state_in_a_captured_step(dtype, tiny_models):
+    """The same decaying sum, written so that a decode step can be captured: single tokens
+    index the state by `seq_slot` on the device. Three sequences in the bucket of four: the
+    padding sequence reads and writes the state store's spare row, never a live sequence's,
+    and the run that precedes a capture touches no state at all (it would count a token
+    twice). Replayed steps against the plain sum."""
+    from lumenllm_b200 import Engine, StepEntry
+    from lumenllm_b200.config import PartSpec
+    from lumenllm_b200.parts import Linear, register_part
+    from lumenllm_b200.sampling import SamplingConfig
+
+    @register_part("mixer", "toy_decaying_sum_on_device")
+    class DecayingSumOnDevice:
+        graph_safe = True
+
+        @classmethod
+        def tensors(cls, spec):
+            H = spec.params["hidden_size"]
+            return {f"{spec.prefix}.mix.weight": ((H, H), "matrix")}
+
+        def __init__(self, spec, weights, runtime):
+            self.decay = float(spec.params["decay"])
+            self.H = spec.params["hidden_size"]
+            self.mix = Linear(weights[f"{spec.prefix}.mix.weight"], runtime)
+            self.runtime = runtime
+
+        def cache_need(self):
+            return None
+
+        def state_shape(self):
+            return (self.H,), torch.float32
+
+        def forward(self, y, ctx, entry):
+            state = entry.state()                       # [max_slots + 1, H]
+            if ctx.is_decode:                           # one token each: device indices only
+                rows = ctx.seq_slot.long()
+                s = state.index_select(0, rows) * self.decay + y.float()
+                state.index_copy_(0, rows, s)
+                return self.mix(s.to(self.runtime.dtype))
+            out = torch.empty(y.shape, dtype=torch.float32, device=y.device)
+            n = 0
+            for b in range(ctx.n_real):
+                s = state[ctx.slots[b]]
+                for t in range(ctx.q_lens[b]):
+                    s.mul_(self.decay).add_(y[n].float())
+                    out[n] = s
+                    n += 1
+            return self.mix(out.to(self.runtime.dtype))
+
+    base = spec_of("B")
+    toy = PartSpec("toy_decaying_sum_on_device", {"hidden_size": 96, "decay": 0.75}, prefix="model.layers.1.toy")
+    layers = list(base.layers)
+    layers[1] = replace(layers[1], mixer=toy)
+    spec = replace(base, layers=tuple(layers))
+    w = gpu_weights(tiny_models["B"])
+    w["model.layers.1.toy.mix.weight"] = (0.05 * torch.randn(96, 96, generator=torch.Generator().manual_seed(4))
+                                          ).to(torch.bfloat16).cuda()
+    wf = {k: v.float().cpu() for k, v in w.items()}
+    name = "float32" if dtype == F32 else "bfloat16"
+    eng = Engine(spec, w, dtype=name, max_tokens=2048, max_slots=6)
+    assert eng.model.graph_safe
+    cfg = TINY["B"]
+
+    def plain(tokens):
+        tokens = torch.tensor(tokens)
+        pos = torch.arange(len(tokens))
+        h = P.embed(tokens, wf["model.embed_tokens.weight"])
+        for i in range(3):
+            if i != 1:
+                h = P.decoder_layer(h, wf, i, cfg, pos)
+                continue
+            p = "model.layers.1."
+            y = P.rms_norm(h, wf[p + "input_layernorm.weight"], 1e-5)
+            s = torch.zeros(96)
+            rows = []
+            for t in range(len(tokens)):
+                s = s * 0.75 + y[t]
+                rows.append(s)
+            r = h + torch.stack(rows) @ wf[p + "toy.mix.weight"].T
+            h = r + P.mlp_block(P.rms_norm(r, wf[p + "post_attention_layernorm.weight"], 1e-5), wf, p)
+        return P.rms_norm(h, wf["model.norm.weight"], 1e-5) @ wf["lm_head.weight"].T
+
+    seqs = seeded_tokens(384, [30, 9, 17], 5)
+    refs = [plain(q) for q in seqs]
+    hold = [eng.alloc_slot() for _ in range(3)]        # the live sequences get the LAST slots,
+    slots = [eng.alloc_slot() for _ in seqs]           # next to the spare row
+    cuts = [20, 2, 10]
+    eng.step([StepEntry(s, q[:c], []) for s, q, c in zip(slots, seqs, cuts)])
+    state = eng.cache.state.of(1)
+    for t in range(7):
+        n = len(seqs)
+        eng.run_device([(s, [q[c + t]]) for s, q, c in zip(slots, seqs, cuts)], [SamplingConfig()] * n, [0.0] * n)
+        cap = eng.graphs.last
+        assert cap.ctx.B == 4
+        got = cap.logits[:n].float().cpu()
+        for k in range(n):
+            ref = refs[k][cuts[k] + t:cuts[k] + t + 1]
+            assert float((got[k:k + 1] - ref).abs().max()) < tolerance(name, ref), (t, k)
+    for s in hold:                                     # sequences that never ran: state untouched
+        assert float(state[s].abs().max()) == 0.0
+    for s in hold + slots:
+        eng.free_slot(s)
+    eng.cache.check()
+
+
 def _step_whole_tail_and_batch(eng, seqs, cuts):
     """Logits of every position of each sequence: prompts of cuts[i] tokens in one batch, the
     rest token by token, shorter sequences ending earlier; slots are freed as they end."""

@@ -12,8 +12,10 @@ from lumenllm_b200.weights import (WeightError, load_weights, open_checkpoint, r
 
 
 def _expected(name):
+    """(shapes of the tensors the model must find, kinds of all it reads)."""
     spec = config_from_dict(TINY[name]).model_spec()
-    return {n: s for n, (s, _) in expected_tensors(spec).items()}, expected_tensors(spec)
+    kinds = expected_tensors(spec)
+    return {n: s for n, (s, k) in kinds.items() if k != "optional"}, kinds
 
 
 def test_random_model_reads_back_by_name(tiny_models):
@@ -29,17 +31,73 @@ def test_random_model_reads_back_by_name(tiny_models):
         assert cfg["hidden_size"] == TINY[name]["hidden_size"]
 
 
-def test_tied_head_has_no_tensor():
-    expA, _ = _expected("A")
+def test_tied_head_has_no_tensor_of_its_own():
+    expA, kindsA = _expected("A")
     expB, _ = _expected("B")
     assert "lm_head.weight" not in expA and "lm_head.weight" in expB
+    assert kindsA["lm_head.weight"][1] == "optional"
+    assert "lm_head.weight" not in random_weights(kindsA, 1, 0.05, 0.1, torch.float32)
+
+
+def test_the_head_is_chosen_by_what_the_file_stores(tmp_path):
+    """As the reference does (executor/full.rs:171-181): a stored lm_head.weight is the head,
+    whatever config.json says about tying; without one the embedding is."""
+    from lumenllm_b200.engine.model import tensor_fallbacks
+    from lumenllm_b200.parts import build_part
+    from lumenllm_b200.parts.base import Runtime
+    rt = Runtime(torch.device("cpu"), torch.float32)
+    # tied by config.json, and the file stores a head all the same
+    spec = config_from_dict(TINY["A"]).model_spec()
+    kinds = expected_tensors(spec)
+    t = random_weights(kinds, 3, 0.05, 0.1, torch.bfloat16)
+    t["lm_head.weight"] = torch.randn(kinds["lm_head.weight"][0]).to(torch.bfloat16)
+    write_file(tmp_path / "model.safetensors", t)
+    shapes = {n: s for n, (s, _) in kinds.items()}
+    w = load_weights(tmp_path, shapes, "cpu", optional=["lm_head.weight"], fallbacks=tensor_fallbacks(spec))
+    assert torch.equal(build_part("head", spec.head, w, rt).proj.weight, t["lm_head.weight"])
+    del t["lm_head.weight"]
+    write_file(tmp_path / "model.safetensors", t)
+    w = load_weights(tmp_path, shapes, "cpu", optional=["lm_head.weight"], fallbacks=tensor_fallbacks(spec))
+    assert "lm_head.weight" not in w and not w.stood_in
+    assert torch.equal(build_part("head", spec.head, w, rt).proj.weight, t["model.embed_tokens.weight"])
+    # untied by config.json, and the file stores no head
+    spec = config_from_dict(TINY["B"]).model_spec()
+    kinds = expected_tensors(spec)
+    shapes = {n: s for n, (s, _) in kinds.items()}
+    t = random_weights(kinds, 3, 0.05, 0.1, torch.bfloat16)
+    del t["lm_head.weight"]
+    write_file(tmp_path / "model.safetensors", t)
+    with pytest.raises(WeightError, match="missing tensors"):
+        load_weights(tmp_path, shapes, "cpu")
+    w = load_weights(tmp_path, shapes, "cpu", fallbacks=tensor_fallbacks(spec))
+    assert w.stood_in == {"lm_head.weight": "model.embed_tokens.weight"}
+    assert torch.equal(build_part("head", spec.head, w, rt).proj.weight, t["model.embed_tokens.weight"])
+
+
+def test_harmless_extras_and_the_strict_switch(tmp_path):
+    exp, kinds = _expected("B")
+    t = random_weights(kinds, 3, 0.05, 0.1, torch.bfloat16)
+    t["model.layers.0.self_attn.rotary_emb.inv_freq"] = torch.randn(16)
+    write_file(tmp_path / "model.safetensors", t)
+    assert load_weights(tmp_path, exp, "cpu").unexpected == []      # a table nobody reads
+    t["model.layers.0.extra.weight"] = torch.randn(2)
+    write_file(tmp_path / "model.safetensors", t)
+    with pytest.raises(WeightError, match="unexpected tensors") as ei:
+        load_weights(tmp_path, exp, "cpu")
+    assert ei.value.unexpected == ["model.layers.0.extra.weight"]
+    w = load_weights(tmp_path, exp, "cpu", strict=False)
+    assert w.unexpected == ["model.layers.0.extra.weight"] and set(w) == set(exp)
+    del t["model.norm.weight"]                 # a missing tensor stays fatal without strict
+    write_file(tmp_path / "model.safetensors", t)
+    with pytest.raises(WeightError, match="missing tensors"):
+        load_weights(tmp_path, exp, "cpu", strict=False)
 
 
 def test_values_do_not_depend_on_order():
     _, kinds = _expected("A")
     a = random_weights(kinds, 5, 0.05, 0.1, torch.float32)
     b = random_weights(dict(reversed(list(kinds.items()))), 5, 0.05, 0.1, torch.float32)
-    assert all(torch.equal(a[n], b[n]) for n in kinds)
+    assert all(torch.equal(a[n], b[n]) for n in a) and set(a) == set(b)
     c = random_weights(kinds, 6, 0.05, 0.1, torch.float32)
     assert not torch.equal(a["model.norm.weight"], c["model.norm.weight"])
     assert float((a["model.norm.weight"] - 1).abs().max()) <= 0.1
@@ -58,8 +116,8 @@ def test_kept_dtypes(tmp_path):
 
 def test_one_error_lists_everything(tmp_path, tiny_models):
     exp, _ = _expected("B")
-    from tests_helpers import read_all
-    tensors = read_all(tiny_models["B"] / "model.safetensors")
+    import plain_qwen3 as P
+    tensors = P.read_safetensors(tiny_models["B"] / "model.safetensors")
     del tensors["model.layers.1.mlp.up_proj.weight"]
     del tensors["model.norm.weight"]
     tensors["model.layers.0.self_attn.q_proj.weight"] = torch.zeros(7, 96, dtype=torch.bfloat16)
