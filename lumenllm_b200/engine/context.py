@@ -123,15 +123,20 @@ class StepLayout:
         return cls(B, N, W, width, n_groups, offs, offs[-1])
 
 
-def pack_step(cache, entries, pad_to: int = 0, table_width: int = 0, want_padding: bool = False):
+def pack_step(cache, entries, pad_to: int = 0, table_width: int = 0, want_padding: bool = False,
+              pad_lens: Optional[Sequence[int]] = None):
     """Reserves cache room for the entries and lays the step's metadata out on the host.
-    With pad_to > len(entries), padding sequences of one token are appended: they write
-    to the reserved page 0 and are read by nobody (with want_padding their logits are
-    computed too, so that a captured step keeps its shapes)."""
+    With pad_to > len(entries), padding sequences are appended (of one token each, or of
+    pad_lens[i] tokens, which may be none): they start at position 0, their page table is all zeros, so they
+    write to the reserved page 0 and are read by nobody (with want_padding the logits at
+    their first token are computed too, so that a captured step keeps its shapes)."""
     starts = [cache.reserve(e.slot, len(e.tokens)) for e in entries]
     B_real = len(entries)
     B = max(B_real, pad_to)
-    q_lens = [len(e.tokens) for e in entries] + [1] * (B - B_real)
+    pads = [1] * (B - B_real) if pad_lens is None else [int(x) for x in pad_lens]
+    if len(pads) != B - B_real or any(x < 0 for x in pads):
+        raise ValueError("pad_lens: one length for each padding sequence")
+    q_lens = [len(e.tokens) for e in entries] + pads
     starts_all = starts + [0] * (B - B_real)
     # padding sequences point at the state store's spare row, as their writes go to page 0
     slots = [e.slot for e in entries] + [cache.state.pad_row] * (B - B_real)
@@ -158,7 +163,7 @@ def pack_step(cache, entries, pad_to: int = 0, table_width: int = 0, want_paddin
                 want[w] = n + int(x)
                 w += 1
         elif want_padding:
-            want[w] = n
+            want[w] = n if q > 0 else 0        # an empty padding sequence has no row of its own
             w += 1
         pos = np.arange(starts_all[b], starts_all[b] + q, dtype=np.int32)
         given = entries[b].positions if b < B_real else None
@@ -177,6 +182,25 @@ def pack_step(cache, entries, pad_to: int = 0, table_width: int = 0, want_paddin
         for b in range(B_real):
             bt[b, :wcols] = g.table[slots[b], :wcols]
     return host, lay, q_lens, starts_all, slots, B_real
+
+
+def padding_twin(host: np.ndarray, lay: StepLayout, q_lens, pad_row: int) -> np.ndarray:
+    """The metadata of a step with the same division of tokens in which EVERY sequence is a
+    padding sequence (token 0, positions from 0, page table of zeros, the state store's spare
+    row): what a captured step is run on once before its capture, so that this run changes
+    nothing that belongs to a live sequence."""
+    offs = lay.offs
+    twin = host.copy()
+    N, B = lay.N, lay.B
+    twin[offs[0]:offs[0] + N] = 0
+    pos = np.concatenate([np.arange(q, dtype=np.int32) for q in q_lens])
+    twin[offs[1]:offs[1] + N] = pos
+    twin[offs[2]:offs[2] + N] = pos
+    twin[offs[4]:offs[4] + B] = pad_row
+    twin[offs[5]:offs[5] + B] = 0
+    for gi in range(lay.n_groups):
+        twin[offs[9 + gi]:offs[9 + gi] + B * lay.width] = 0
+    return twin
 
 
 def context_on(dev: torch.Tensor, lay: StepLayout, q_lens, starts, slots, n_real, cache, runtime):

@@ -79,8 +79,8 @@ class Engine:
         self.sampler = DeviceSampler(self.device)
         self._meta_dev = torch.empty((1 << 16,), dtype=torch.int32, device=self.device)
         self.steps_run = 0
-        from .decode_graph import DecodeGraphs
-        self.graphs = DecodeGraphs(self)
+        from .step_graph import StepGraphs
+        self.graphs = StepGraphs(self)
         self.use_graphs = bool(use_graphs)
 
     # ------------------------------------------------------------ construction
@@ -246,8 +246,9 @@ class Engine:
 
     def run_device(self, entries, configs, uniforms, tokens_on_device=None) -> torch.Tensor:
         """As `run`, but the sampled tokens stay on the device (int32 [len(entries)])."""
-        if self.use_graphs and self.model.graph_safe and all(len(t) == 1 for _, t in entries):
-            self._validate([StepEntry(s, t, [0]) for s, t in entries])
+        if self.use_graphs and self.model.graph_safe and all(t is not None and len(t) for _, t in entries) \
+                and self.graphs.takes([len(t) for _, t in entries]):
+            self._validate([StepEntry(s, t, [len(t) - 1]) for s, t in entries])
             try:
                 return self.graphs.step(entries, configs, uniforms, tokens_on_device)
             except CacheFull as e:

@@ -379,14 +379,17 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
 
 
 def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window, scale,
-                 tensor_memory=True):
+                 tensor_memory=True, n_seqs=None):
     """Causal flash attention for sequences that bring q_lens[b] tokens each (host list),
     bfloat16, swizzled cache, head size 64 or 128, at most 16 query heads per kv head.
     q [N, nq, d]; cu_q int32 [B+1]; seq_start int32 [B]. With tensor_memory the tcgen05
-    kernel (128 rows a block, S and O in tensor memory), else the mma.sync kernel (64 rows)."""
+    kernel (128 rows a block, S and O in tensor memory), else the mma.sync kernel (64 rows).
+    With q_lens None and n_seqs = B the host need not know how the N tokens are divided (a
+    captured step does not): enough blocks are launched for any division, every block finds
+    its sequence and tile from cu_q on the device, and the blocks left over return at once."""
     N, nq, d = q.shape
     nkv = kcache.shape[1]
-    B = len(q_lens)
+    B = len(q_lens) if q_lens is not None else int(n_seqs)
     require(q, BF16, "attn_prefill.q")
     require(kcache, BF16, "attn_prefill.kcache")
     require(vcache, BF16, "attn_prefill.vcache")
@@ -395,10 +398,12 @@ def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window
     require(seq_start, I32, "attn_prefill.seq_start")
     if nq % nkv or nq // nkv > 16:
         raise KernelError("attn_prefill: at most 16 query heads per kv head")
-    if cu_q.numel() < B + 1 or seq_start.numel() < B or block_table.shape[0] < B or sum(q_lens) != N:
+    if cu_q.numel() < B + 1 or seq_start.numel() < B or block_table.shape[0] < B or \
+            (q_lens is not None and sum(q_lens) != N):
         raise KernelError("attn_prefill: metadata does not match the batch")
     tq = (128 if tensor_memory else 64) // (nq // nkv)
-    n_tiles = sum((n + tq - 1) // tq for n in q_lens)
+    # sum of ceil(q_b / tq) over any division of N tokens into B sequences is at most N // tq + B
+    n_tiles = sum((n + tq - 1) // tq for n in q_lens) if q_lens is not None else N // tq + B
     out = torch.empty_like(q)
     f = fn("attn_prefill_tc" if tensor_memory else "attn_prefill",
            "lumen_attn_prefill_tc" if tensor_memory else "lumen_attn_prefill",

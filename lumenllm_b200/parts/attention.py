@@ -111,7 +111,10 @@ class GQAttention:
         if fast and ctx.is_decode:
             return K.attn_decode(q, kc, vc, table, ctx.cache_pos, self.window, self.scale)
         if fast:
-            return K.attn_prefill(q, kc, vc, table, ctx.cu_q, ctx.seq_start, ctx.q_lens, self.window,
-                                  self.scale)
+            # a captured step is replayed for other divisions of its tokens than the one it was
+            # captured with: the kernel then takes the division from the device alone
+            q_lens = None if ctx.extras.get("captured") else ctx.q_lens
+            return K.attn_prefill(q, kc, vc, table, ctx.cu_q, ctx.seq_start, q_lens, self.window,
+                                  self.scale, n_seqs=ctx.B)
         return K.attn_generic(q, kc, vc, table, ctx.tok_seq, ctx.cache_pos, self.window, self.scale,
                               layout=layout)

@@ -174,7 +174,60 @@ def test_long_decoding(name, dtype, how, plain, engines):
     eng = engines(name, dtype)
     check(run_tail(eng, seq, tail=400, decode=DECODERS[how]), ref, dtype, f"{name} long decode")
     if how == "captured":
-        assert {k[1] for k in eng.graphs.captured if k[0] == 1} >= {1, 2, 4, 8}
+        assert {k[2] for k in eng.graphs.captured if k[:2] == (1, 1)} >= {1, 2, 4, 8}
+
+
+def captured_step(eng, pairs):
+    """[(slot, tokens)] through the captured step (prompts or single tokens): the logits at
+    each sequence's last token, and the captured step that was replayed."""
+    from lumenllm_b200.sampling import SamplingConfig
+    n = len(pairs)
+    eng.run_device(pairs, [SamplingConfig()] * n, [0.0] * n)
+    cap = eng.graphs.last
+    return cap.logits[:n].float().cpu(), cap
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("name", NAMES)
+def test_captured_prompt_steps(name, dtype, plain, engines, tiny_models):
+    """Prompts of unequal lengths through the captured prompt step, the way generation feeds
+    them: a batch that captures a step for its buckets (128 tokens, 4 sequences, 2 pages); a
+    second batch with another division of its tokens that replays the same captured step on
+    the slots and pages the first gave back; a piece that continues cached prompts; then
+    single tokens. Against the plain implementation, and bit for bit against the same steps
+    launched kernel by kernel on a twin engine (padding tokens change nothing)."""
+    from lumenllm_b200 import Engine, StepEntry
+    cfg, w = plain[name]
+    eng = engines(name, dtype)
+    twin = Engine.from_folder(tiny_models[name], dtype=dtype, max_tokens=4096, use_graphs=False)
+    first_cap = None
+    for round_, lens in enumerate(([33, 2, 65], [70, 20, 7])):
+        seqs = seeded_tokens(cfg["vocab_size"], [n + 12 for n in lens], 300 + round_)
+        refs = [plain_ref(cfg, w, q) for q in seqs]
+        slots = [eng.alloc_slot() for _ in seqs]
+        tslots = [twin.alloc_slot() for _ in seqs]
+        lg, cap = captured_step(eng, [(s, q[:n]) for s, q, n in zip(slots, seqs, lens)])
+        assert (cap.ctx.N, cap.ctx.B) == (128, 4)
+        check(lg, Ref.cat([r[n - 1:n] for r, n in zip(refs, lens)]), dtype, f"{name} captured prompts {lens}")
+        eager = twin.step([StepEntry(s, q[:n], [n - 1]) for s, q, n in zip(tslots, seqs, lens)]).cpu()
+        assert torch.equal(lg, eager), f"{name} {lens}: captured and eager prompt step differ"
+        if first_cap is None:
+            first_cap = cap
+        else:
+            assert cap is first_cap                  # replayed, not captured again
+        # nine more tokens of each prompt on top of what is cached, then three single tokens
+        lg, cap = captured_step(eng, [(s, q[n:n + 9]) for s, q, n in zip(slots, seqs, lens)])
+        assert cap.ctx.N == 32
+        check(lg, Ref.cat([r[n + 8:n + 9] for r, n in zip(refs, lens)]), dtype, f"{name} captured continuation {lens}")
+        for t in range(9, 12):
+            lg = captured_decode(eng, [(s, q[n + t]) for s, q, n in zip(slots, seqs, lens)])
+            check(lg, Ref.cat([r[n + t:n + t + 1] for r, n in zip(refs, lens)]), dtype,
+                  f"{name} token {t} after captured prompts {lens}")
+        for s in slots:
+            eng.free_slot(s)
+        for s in tslots:
+            twin.free_slot(s)
+        eng.cache.check()
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
@@ -203,7 +256,7 @@ def test_a_padded_captured_batch_equals_the_eager_step(name, dtype, plain, tiny_
         assert torch.equal(a, b), f"{name} step {t}: replay and eager step differ"
         for k in range(3):
             check(a[k:k + 1], refs[k][cuts[k] + t:cuts[k] + t + 1], dtype, f"{name} step {t} request {k}")
-    assert len({key[1] for key in twins[0].graphs.captured}) >= 2
+    assert len({key[2] for key in twins[0].graphs.captured}) >= 2
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
