@@ -2,8 +2,10 @@
 //
 // One query token per sequence. A block takes one SEGMENT of a sequence (a run of at most
 // seg_pages pages; a sequence's pages are dealt out evenly over its segments) for one kv head and serves all query heads of that kv head at once, so every key and value
-// is read from HBM exactly once per step. The block walks its pages through a three-stage
-// ring: the K tile and the V tile of a page are each one contiguous, already swizzled block
+// is read from HBM exactly once per step. The block walks its pages through a ring of two or
+// three stages (three while all blocks of the launch fit the SMs at once and a deeper ring is
+// what hides latency; two, so that three blocks instead of two share an SM, when there are
+// more blocks than that; the depth changes no result): the K tile and the V tile of a page are each one contiguous, already swizzled block
 // of the cache and are brought in by one bulk asynchronous copy each (cp.async.bulk,
 // completion on an mbarrier), while the tensor cores work on the page before: no tensor
 // map, no address arithmetic per element. Each of the four warps owns 16 keys of a page:
@@ -29,7 +31,7 @@
 #define AD_THREADS 128
 #define AD_SEG_PAGES 8            // the largest seg_pages a caller may ask for
 #define AD_MAX_SEGS 32            // a sequence is never cut into more segments than this
-#define AD_STAGES 3
+#define AD_MAX_STAGES 3           // ring depth: 3 when every block is resident at once, else 2
 
 // The pages [pg_lo, pg_hi] that the query at position p sees, cut into nseg segments of
 // per or per + 1 pages (the first rem have one more): segments of seg_pages pages at most,
@@ -53,7 +55,7 @@ __device__ __forceinline__ SegPlan seg_plan(int p, int window, int seg_pages) {
     return s;
 }
 
-template <int D>
+template <int D, int AD_STAGES>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
                    const __nv_bfloat16* __restrict__ vcache, const int* __restrict__ block_table,
@@ -352,20 +354,25 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
     const __nv_bfloat16* kp = (const __nv_bfloat16*)kcache;
     const __nv_bfloat16* vp = (const __nv_bfloat16*)vcache;
     cudaError_t e;
+    static int sms = 0;
+    if (!sms) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
+    }
+    const bool deep = (long long)max_segs * nkv * B <= 2LL * sms;
+    auto go = [&](auto kernel, int stages, int dd) -> cudaError_t {
+        const int smem = stages * 2 * LUMEN_PAGE * dd * 2;
+        cudaError_t err_ = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
+        if (err_ != cudaSuccess) return err_;
+        return lumen_launch(kernel, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride,
+                            seq_pos, part_o, part_ml, nq, nkv, window, scale, max_segs, seg_pages, err, counters,
+                            (__nv_bfloat16*)out);
+    };
     if (d == 128) {
-        const int smem = AD_STAGES * 2 * LUMEN_PAGE * 128 * 2;
-        auto k = attn_decode_kernel<128>;
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        e = lumen_launch(k, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos,
-                         part_o, part_ml, nq, nkv, window, scale, max_segs, seg_pages, err, counters,
-                         (__nv_bfloat16*)out);
+        e = deep ? go(attn_decode_kernel<128, 3>, 3, 128) : go(attn_decode_kernel<128, 2>, 2, 128);
     } else if (d == 64) {
-        const int smem = AD_STAGES * 2 * LUMEN_PAGE * 64 * 2;
-        auto k = attn_decode_kernel<64>;
-        cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
-        e = lumen_launch(k, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, seq_pos,
-                         part_o, part_ml, nq, nkv, window, scale, max_segs, seg_pages, err, counters,
-                         (__nv_bfloat16*)out);
+        e = deep ? go(attn_decode_kernel<64, 3>, 3, 64) : go(attn_decode_kernel<64, 2>, 2, 64);
     } else {
         return LUMEN_ERR_UNSUPPORTED;
     }

@@ -34,6 +34,7 @@
 #define PT_ROWS 128
 #define PT_STAGES 2
 #define PT_RESCALE 8.0f
+#define PT_FMA_EX2_OF_4 1         // of every four exponentials, this many go to the FMA pipe
 
 __device__ __forceinline__ void pt_mbar_arrive(uint64_t* bar) {
     asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
@@ -95,6 +96,20 @@ __device__ __forceinline__ float pt_ex2(float x) {
     float y;
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
+}
+// 2^x without the special-function unit: x = n + f with n the nearest integer (the magic-number
+// add leaves n in the low mantissa bits), 2^f on [-0.5, 0.5] by a cubic (relative error 1e-4,
+// a twentieth of the rounding to bfloat16 that follows), and n added into the exponent bits.
+// The softmax does a part of its exponentials this way: the special-function unit makes 16 a
+// cycle and SM, and at head size 128 that is as long a job as the page's two products.
+__device__ __forceinline__ float pt_ex2_fma(float x) {
+    x = fmaxf(x, -125.0f);                       // also what a masked (-inf) score becomes: 2^-125, nothing
+    const float t = x + 12582912.0f;             // 1.5 * 2^23
+    const float f = x - (t - 12582912.0f);
+    float p = fmaf(0.05583828315138817f, f, 0.2426394820213318f);
+    p = fmaf(p, f, 0.6931367516517639f);
+    p = fmaf(p, f, 0.9999245405197144f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
 }
 __device__ __forceinline__ void pt_st32(uint32_t taddr, const float (&v)[32]) {
     asm volatile(
@@ -356,9 +371,11 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
 #pragma unroll
             for (int j = 0; j < 64; j += 4) {
                 s[j] = pt_ex2(fmaf(s[j], scale_log2, nbase));
-                s[j + 1] = pt_ex2(fmaf(s[j + 1], scale_log2, nbase));
+                s[j + 1] = (PT_FMA_EX2_OF_4 >= 2) ? pt_ex2_fma(fmaf(s[j + 1], scale_log2, nbase))
+                                                  : pt_ex2(fmaf(s[j + 1], scale_log2, nbase));
                 s[j + 2] = pt_ex2(fmaf(s[j + 2], scale_log2, nbase));
-                s[j + 3] = pt_ex2(fmaf(s[j + 3], scale_log2, nbase));
+                s[j + 3] = (PT_FMA_EX2_OF_4 >= 1) ? pt_ex2_fma(fmaf(s[j + 3], scale_log2, nbase))
+                                                  : pt_ex2(fmaf(s[j + 3], scale_log2, nbase));
                 rs4[0] += s[j];
                 rs4[1] += s[j + 1];
                 rs4[2] += s[j + 2];
