@@ -7,10 +7,18 @@
 //               swizzle), S into tensor memory (two S buffers, so the product for the next page
 //               runs while this page's softmax does);
 //   softmax     four warps, one thread per row: tcgen05.ld of the row, scale, mask, running
-//               maximum and sum in float32, P = exp2(.) rounded to bfloat16 and written to
-//               shared memory as the next product's A operand;
-//   O += P V    tcgen05.mma 128 x D x 64, V straight from its page tile (N-major, 128-byte
-//               swizzle: the cache layout is made for this), O accumulated in tensor memory.
+//               maximum and sum in float32, P = exp2(.) rounded to bfloat16 and written back
+//               into tensor memory, over the columns its own scores came from (tcgen05.st);
+//   O += P V    tcgen05.mma 128 x D x 64 with P as the A operand FROM TENSOR MEMORY and V
+//               straight from its page tile in shared memory (N-major, 128-byte swizzle: the
+//               cache layout is made for this), O accumulated in tensor memory.
+// What bounds this kernel at long prompts is neither pipe but the chain of hand-overs of a page
+// (product done -> scores loaded -> P stored -> product issued, each a barrier or a tensor-memory
+// wait): taking the exponentials out altogether makes it 7 % faster, issuing only half of the
+// S products 7 %, half of the O products 6 %; P in tensor memory instead of a 16 KB buffer in
+// shared memory (32 KB less shared-memory traffic a page, and no wait for the product of the
+// page before unless O is rescaled) gave 5 % at 8,192 tokens and 4 % at 2,048, one exponential
+// in four on the FMA pipe another 10 % at 2,048.
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the reference it
 // was accumulated against (P and the row sum use the same reference, so the result is exact);
 // the rescale is a read-modify-write of the row in tensor memory and is rare after the first
@@ -51,6 +59,26 @@ __device__ __forceinline__ void pt_mma(uint32_t d_tmem, uint64_t adesc, uint64_t
         "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
         " tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n}" ::"r"(d_tmem),
         "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+// The same product with the A operand in tensor memory: lane = row, two bfloat16 a column.
+__device__ __forceinline__ void pt_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc,
+                                          uint32_t accumulate) {
+    asm volatile(
+        "{\n .reg .pred p;\n setp.ne.b32 p, %4, 0;\n"
+        " tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n}" ::"r"(d_tmem),
+        "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+__device__ __forceinline__ void pt_st32u(uint32_t taddr, const uint32_t (&v)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], "
+        "{%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};" ::"r"(taddr),
+        "r"(v[0]), "r"(v[1]), "r"(v[2]), "r"(v[3]), "r"(v[4]), "r"(v[5]), "r"(v[6]), "r"(v[7]), "r"(v[8]),
+        "r"(v[9]), "r"(v[10]), "r"(v[11]), "r"(v[12]), "r"(v[13]), "r"(v[14]), "r"(v[15]), "r"(v[16]),
+        "r"(v[17]), "r"(v[18]), "r"(v[19]), "r"(v[20]), "r"(v[21]), "r"(v[22]), "r"(v[23]), "r"(v[24]),
+        "r"(v[25]), "r"(v[26]), "r"(v[27]), "r"(v[28]), "r"(v[29]), "r"(v[30]), "r"(v[31])
         : "memory");
 }
 __device__ __forceinline__ void pt_ld32(uint32_t taddr, float (&v)[32]) {
@@ -158,7 +186,6 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     pdl_trigger();
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;      // one K or V page tile
     constexpr int Q_BYTES = PT_ROWS * D * 2;
-    constexpr int P_BYTES = PT_ROWS * 128;              // 128 rows x 64 keys of bfloat16
     constexpr int NCOLS = 256;                          // S0 | S1 | O
     constexpr uint32_t O_COL = 128;
     // Operand tiles must start on 1024-byte boundaries (the swizzle pattern repeats there).
@@ -171,14 +198,13 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
     }
     unsigned char* sQ = smem;
     unsigned char* sKV = sQ + Q_BYTES;                  // [stage][K tile, V tile]
-    unsigned char* sP = sKV + PT_STAGES * 2 * TILE_BYTES;   // one buffer: the product that read it is awaited
-    uint64_t* bars = reinterpret_cast<uint64_t*>(sP + P_BYTES);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(sKV + PT_STAGES * 2 * TILE_BYTES);
     uint64_t* k_full = bars;                   // [stages] the K tile has landed
     uint64_t* k_empty = bars + PT_STAGES;      // [stages] the S product has read it
     uint64_t* v_full = bars + 2 * PT_STAGES;   // [stages] the V tile has landed
     uint64_t* v_empty = bars + 3 * PT_STAGES;  // [stages] the O product has read it
     uint64_t* s_full = bars + 4 * PT_STAGES;   // [2] S is in tensor memory
-    uint64_t* p_ready = s_full + 2;            // [2] P is in shared memory, O corrected
+    uint64_t* p_ready = s_full + 2;            // [2] P is in tensor memory, O corrected
     uint64_t* pv_done = p_ready + 2;           // [2] the PV product of that page has finished
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(pv_done + 2);
     volatile int* abort_flag = reinterpret_cast<volatile int*>(tmem_slot + 1);
@@ -311,11 +337,12 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 if (!mbar_wait(&p_ready[it & 1], (it >> 1) & 1)) { ok = false; break; }
                 pt_fence_after();
                 const uint32_t vt = smem_u32(sKV + st * 2 * TILE_BYTES + TILE_BYTES);
-                const uint32_t pt = smem_u32(sP);
+                // P of this page lies over the first 32 columns of the S buffer it was made from
+                const uint32_t pt = tmem_base + (it & 1) * LUMEN_PAGE;
 #pragma unroll
-                for (int kk = 0; kk < LUMEN_PAGE / 16; ++kk)     // 16 keys a step
-                    pt_mma(tmem_base + O_COL, pt_desc(pt + kk * 32, 16),
-                           pt_desc(vt + kk * (16 * 128), LUMEN_PAGE * 128), idesc_pv, (it > 0 || kk > 0) ? 1u : 0u);
+                for (int kk = 0; kk < LUMEN_PAGE / 16; ++kk)     // 16 keys a step: 8 columns of P
+                    pt_mma_ts(tmem_base + O_COL, pt + kk * 8,
+                              pt_desc(vt + kk * (16 * 128), LUMEN_PAGE * 128), idesc_pv, (it > 0 || kk > 0) ? 1u : 0u);
                 pt_commit(&v_empty[st]);
                 pt_commit(&pv_done[it & 1]);
             }
@@ -382,36 +409,29 @@ attn_prefill_tc_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16*
                 rs4[3] += s[j + 3];
             }
             l = l * corr + ((rs4[0] + rs4[1]) + (rs4[2] + rs4[3]));
-            // the PV product of the page before must be done: it reads the P buffer that is
-            // about to be overwritten and it is accumulating into O
-            if (it > 0) {
+            // O is rescaled rarely; only then must the PV product of the page before be done (it
+            // is accumulating into O). P needs no such wait: it goes where this page's scores
+            // were, and the product that read the P of two pages ago finished before these
+            // scores were made (the tensor pipe runs its products in the order of issue).
+            if (it > 0 && __any_sync(0xffffffffu, corr != 1.0f)) {
                 w = mbar_wait(&pv_done[(it - 1) & 1], ((it - 1) >> 1) & 1);
                 if (!__all_sync(0xffffffffu, w)) { ok = false; break; }
                 pt_fence_after();
-                if (__any_sync(0xffffffffu, corr != 1.0f)) {
 #pragma unroll 1
-                    for (int c0 = 0; c0 < D; c0 += 32) {
-                        float ov[32];
-                        pt_ld32(lane_addr + O_COL + c0, ov);
+                for (int c0 = 0; c0 < D; c0 += 32) {
+                    float ov[32];
+                    pt_ld32(lane_addr + O_COL + c0, ov);
 #pragma unroll
-                        for (int j = 0; j < 32; ++j) ov[j] *= corr;
-                        pt_st32(lane_addr + O_COL + c0, ov);
-                    }
-                    asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+                    for (int j = 0; j < 32; ++j) ov[j] *= corr;
+                    pt_st32(lane_addr + O_COL + c0, ov);
                 }
             }
-            // P row: 64 bfloat16 = 8 chunks of 16 bytes, chunk c at c ^ (row & 7)
-            unsigned char* prow_ptr = sP + r * 128;
+            // P row: 64 bfloat16, two a column, keys in rising order
+            uint32_t pk[32];
 #pragma unroll
-            for (int c = 0; c < 8; ++c) {
-                uint4 v;
-                v.x = pack_bf16(s[8 * c], s[8 * c + 1]);
-                v.y = pack_bf16(s[8 * c + 2], s[8 * c + 3]);
-                v.z = pack_bf16(s[8 * c + 4], s[8 * c + 5]);
-                v.w = pack_bf16(s[8 * c + 6], s[8 * c + 7]);
-                *reinterpret_cast<uint4*>(prow_ptr + ((c ^ (r & 7)) << 4)) = v;
-            }
-            asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+            for (int c = 0; c < 32; ++c) pk[c] = pack_bf16(s[2 * c], s[2 * c + 1]);
+            pt_st32u(lane_addr + (it & 1) * LUMEN_PAGE, pk);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             pt_fence_before();
             __syncwarp();
             if (lane == 0) pt_mbar_arrive(&p_ready[it & 1]);
@@ -471,14 +491,14 @@ LUMEN_API int lumen_attn_prefill_tc(const void* q, const void* kcache, const voi
     const __nv_bfloat16* vp = (const __nv_bfloat16*)vcache;
     cudaError_t e;
     if (d == 128) {
-        const int smem = PT_ROWS * 128 * 2 + PT_STAGES * 2 * LUMEN_PAGE * 128 * 2 + PT_ROWS * 128 + 256;
+        const int smem = PT_ROWS * 128 * 2 + PT_STAGES * 2 * LUMEN_PAGE * 128 * 2 + 256;
         auto k = attn_prefill_tc_kernel<128>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
         e = lumen_launch(k, grid, dim3(PT_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride, cu_q,
                          seq_start, B, (__nv_bfloat16*)out, nq, nkv, window, scale_log2, err);
     } else if (d == 64) {
-        const int smem = PT_ROWS * 64 * 2 + PT_STAGES * 2 * LUMEN_PAGE * 64 * 2 + PT_ROWS * 128 + 256;
+        const int smem = PT_ROWS * 64 * 2 + PT_STAGES * 2 * LUMEN_PAGE * 64 * 2 + 256;
         auto k = attn_prefill_tc_kernel<64>;
         e = cudaFuncSetAttribute(k, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
         if (e != cudaSuccess) return (int)e;
