@@ -12,13 +12,20 @@
 //   O += P V    tcgen05.mma 128 x D x 64 with P as the A operand FROM TENSOR MEMORY and V
 //               straight from its page tile in shared memory (N-major, 128-byte swizzle: the
 //               cache layout is made for this), O accumulated in tensor memory.
-// What bounds this kernel at long prompts is neither pipe but the chain of hand-overs of a page
-// (product done -> scores loaded -> P stored -> product issued, each a barrier or a tensor-memory
-// wait): taking the exponentials out altogether makes it 7 % faster, issuing only half of the
-// S products 7 %, half of the O products 6 %; P in tensor memory instead of a 16 KB buffer in
-// shared memory (32 KB less shared-memory traffic a page, and no wait for the product of the
-// page before unless O is rescaled) gave 5 % at 8,192 tokens and 4 % at 2,048, one exponential
-// in four on the FMA pipe another 10 % at 2,048.
+// What bounds this kernel at long prompts is the time the tensor pipe takes over products of
+// these shapes, read off clock stamps taken inside the kernel: the thread that issues them is
+// held 75 cycles by each 128 x 64 x 16 product of S (32 cycles of arithmetic; 6 KB of operands
+// from shared memory) and 92 by each 128 x 128 x 16 product of O (64 of arithmetic), with one
+// block on the SM as with two, so a page costs 970 cycles of the pipe and two blocks an SM fill
+// it (1,860 cycles a page and block). The softmax of a page takes a warp 875 cycles alone and
+// about 1,000 beside its neighbour's, so it is not far behind: without any exponentials the
+// kernel is 7 % faster, with half of the S products 7 %, with half of the O products 6 %.
+// What was gained here: P in tensor memory instead of a 16 KB buffer in shared memory (no
+// write and read of P through shared memory, and no wait for the product of the page before
+// unless O is rescaled) 5 % at 8,192 tokens and 4 % at 2,048; one exponential in four on the
+// FMA pipe 10 % at 2,048. Making the operand descriptors once instead of per product changed
+// nothing. What is left to do is products with more columns: S over two pages at a time
+// (128 x 128 x 16: a third fewer cycles a key) for two Q tiles of one block in turn.
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the reference it
 // was accumulated against (P and the row sum use the same reference, so the result is exact);
 // the rescale is a read-modify-write of the row in tensor memory and is rare after the first
