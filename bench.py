@@ -304,6 +304,8 @@ def main() -> int:
                     help="fewer layers than the shape has, for small memory (named in config)")
     ap.add_argument("--batch", type=int, default=None)
     ap.add_argument("--no-points", action="store_true", help="skip batch 1 and 64")
+    ap.add_argument("--points", default="1,64", metavar="B,B",
+                    help="batch sizes of the further decode points (default 1,64)")
     ap.add_argument("--timings", action="store_true",
                     help="add each kernel class's share of a decode and of a prompt step")
     ap.add_argument("--context", type=int, default=None,
@@ -339,7 +341,8 @@ def main() -> int:
     pk = peaks()
     cfg = dict(shape, num_hidden_layers=layers)
     B = args.batch or wl["batch"]
-    top_b = B if args.no_points else max(B, 64)
+    point_batches = [] if args.no_points else [int(x) for x in args.points.split(",") if x.strip()]
+    top_b = max([B] + point_batches)
     max_tokens = max(B * CONTEXT, top_b * (PROMPT_HI + 64 + warmup + steps + 64))
     nums = model_numbers(cfg, layers)
     need = max_tokens * nums["kv_bytes_per_token"] + 2 * (nums["layer_params"] + 2 * nums["head_params"])
@@ -378,8 +381,8 @@ def main() -> int:
     e2e = e2e_runs[1]
     e2e["window"] = (min(r["window"][0] for r in e2e_runs), max(r["window"][1] for r in e2e_runs))
     points, points_frac, windows = {}, {}, [main_run["window"], e2e["window"]] + pre_windows
-    if not args.no_points:
-        for b in (1, 64):
+    if point_batches:
+        for b in point_batches:
             r = decode_run(eng, b, min(steps, 32), warmup, seed=10 + b)
             points[f"decode_b{b}"] = round(r["tok_s"], 1)
             got = (weight_bytes + b * r["mean_len"] * nums["kv_bytes_per_token"]) / (r["ms"] * 1e-3) / 1e9

@@ -39,6 +39,8 @@ def _engine_flags(ap):
     ap.add_argument("--dtype", choices=["bfloat16", "float32"])
     ap.add_argument("--kv-max-tokens", type=int, help="tokens the cache holds (default ctx x batch)")
     ap.add_argument("--batch-size", type=int)
+    ap.add_argument("--allow-extra-tensors", action="store_true",
+                    help="warn about stored tensors that no part of the model reads instead of refusing them")
 
 
 def _generate_flags(ap):
@@ -60,7 +62,8 @@ def _build(args):
     from .engine import EngineConfig, build
     return build(EngineConfig(model_path=args.model, parameters=args.parameters, dtype=args.dtype,
                               context_size=args.ctx_size, max_tokens=args.kv_max_tokens,
-                              max_batch=args.batch_size, device=args.cuda_device))
+                              max_batch=args.batch_size, device=args.cuda_device,
+                              strict_weights=not args.allow_extra_tensors))
 
 
 def _requests(args, built):

@@ -30,6 +30,7 @@ class EngineConfig:
     max_batch: Optional[int] = None
     device: Optional[int] = None
     sampling: Optional[SamplingDefaults] = None
+    strict_weights: bool = True             # False: stored tensors that no part reads are warned about
 
 
 @dataclass
@@ -71,7 +72,7 @@ def build(cfg: EngineConfig) -> BuiltEngine:
     device = cfg.device if cfg.device is not None else pf.device
     common = dict(dtype=dtype, max_tokens=max_tokens, device=device, context_size=ctx)
     if model_path is not None:
-        eng = Engine.from_folder(model_path, **common)
+        eng = Engine.from_folder(model_path, strict_weights=cfg.strict_weights, **common)
     else:
         seed = cfg.random_seed if cfg.random_config else pf.random_seed
         eng = Engine.from_random(random_config, seed=seed, **common)

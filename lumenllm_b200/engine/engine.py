@@ -101,6 +101,14 @@ class Engine:
             warnings.warn(f"{folder}: no tensor '{name}' is stored; '{other}' stands in for it")
         for name in weights.unexpected:
             warnings.warn(f"{folder}: tensor '{name}' is stored but no part of the model reads it")
+        if _DTYPES.get(dtype) == torch.bfloat16:
+            wide = [n for n, (_, kind) in tensors.items()
+                    if kind != "norm" and n in weights and weights[n].dtype == torch.float32]
+            if wide:
+                # a tensor stored in 32-bit stays so, and its products then run in true 32-bit
+                warnings.warn(f"{folder}: {len(wide)} matrices are stored in 32-bit (first: '{wide[0]}'); "
+                              "they are kept so and multiplied by the 32-bit kernel, many times slower "
+                              "than the tensor cores. Store the checkpoint in bfloat16 to serve it.")
         return cls(spec, weights, dtype, max_tokens, max_slots, dev.index, config=config, **kw)
 
     @classmethod
