@@ -24,8 +24,15 @@
 // write and read of P through shared memory, and no wait for the product of the page before
 // unless O is rescaled) 5 % at 8,192 tokens and 4 % at 2,048; one exponential in four on the
 // FMA pipe 10 % at 2,048. Making the operand descriptors once instead of per product changed
-// nothing. What is left to do is products with more columns: S over two pages at a time
-// (128 x 128 x 16: a third fewer cycles a key) for two Q tiles of one block in turn.
+// nothing. Products with more columns were tried as a kernel of its own: one block an SM
+// with two Q tiles that share their K and V tiles, keys 128 at a time, S and O of both tiles
+// in all 512 columns of tensor memory, the tiles taken in turn by the tensor pipe. Right
+// results, and the S products did cost 66 cycles for 128 columns where they cost 75 for 64;
+// but the O products, whose P operand comes from tensor memory, rose from 92 to 116 cycles
+// under the tensor-memory traffic of eight softmax warps, a tile's chain (softmax of 128
+// scores 2,270 cycles, then its O product, then its next S product) leaves the one issuing
+// thread either held by the pipe or waiting, and a step of four page tiles took 4,100 to
+// 4,300 cycles: 650 us at 8,192 tokens against 544 us for this kernel. Taken out again.
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the reference it
 // was accumulated against (P and the row sum use the same reference, so the result is exact);
 // the rescale is a read-modify-write of the row in tensor memory and is rare after the first
