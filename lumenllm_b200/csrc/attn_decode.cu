@@ -11,7 +11,8 @@
 // map, no address arithmetic per element. Each of the four warps owns 16 keys of a page:
 // S = Q K^T and O = P V run as mma.sync m16n8k16 with the query heads of the group padded to
 // 16 rows (the kernel is bound by HBM; the padding costs nothing), softmax online in
-// float32 per warp across the pages. At the end the block merges its four warps. A sequence
+// float32 per warp across the pages, with scores and running maxima in units of log 2 so that
+// every exponential is one ex2 instruction, and a row's sum kept per lane until the last page. At the end the block merges its four warps. A sequence
 // that fits one segment is finished there; otherwise the block writes one partial
 // (unnormalised O, running max m, sum l) per (sequence, head, segment) and the segments are
 // merged in rising order, either by the block of the group that finishes last (it learns
@@ -31,6 +32,7 @@
 #define AD_THREADS 128
 #define AD_SEG_PAGES 8            // the largest seg_pages a caller may ask for
 #define AD_MAX_SEGS 32            // a sequence is never cut into more segments than this
+#define AD_PAGE_IDS 16             // page numbers of a segment kept in shared memory
 #define AD_MAX_STAGES 3           // ring depth: 3 when every block is resident at once, else 2
 
 // The pages [pg_lo, pg_hi] that the query at position p sees, cut into nseg segments of
@@ -55,6 +57,14 @@ __device__ __forceinline__ SegPlan seg_plan(int p, int window, int seg_pages) {
     return s;
 }
 
+// 2^x on the special-function unit (2 ulp); scores and running maxima are kept in units of
+// log 2, so every exponential of the softmax and of the merges is one instruction
+__device__ __forceinline__ float ad_ex2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 template <int D, int AD_STAGES>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
@@ -68,6 +78,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     __shared__ uint64_t full[AD_STAGES];
     __shared__ float s_m[4][16], s_l[4][16];
     __shared__ int s_last;
+    __shared__ int s_page[AD_PAGE_IDS];       // the segment's first page numbers, read once
 
     const int seg = blockIdx.x, kvh = blockIdx.y, b = blockIdx.z;
     const int p = seq_pos[b];                   // written before the step's first kernel
@@ -84,9 +95,15 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         for (int i = 0; i < AD_STAGES; ++i) mbar_init(&full[i], 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
+    // The page table was written before the step's first kernel: the segment's page numbers
+    // are fetched once, all at the same time, instead of one dependent load from global
+    // memory in front of every copy (which held the whole block some 700 cycles a page).
+    if (tid < AD_PAGE_IDS && tid < npages) s_page[tid] = bt[pg_a + tid];
     __syncthreads();
     auto issue = [&](int stage, int pg) {
-        const size_t off = ((size_t)bt[pg] * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+        const int idx = pg - pg_a;
+        const int page = idx < AD_PAGE_IDS ? s_page[idx] : bt[pg];
+        const size_t off = ((size_t)page * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
         unsigned char* dst = smem + stage * 2 * TILE_BYTES;
         mbar_expect_tx(&full[stage], 2 * TILE_BYTES);
         bulk_load(dst, kcache + off, TILE_BYTES, &full[stage]);
@@ -169,23 +186,21 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 2));
         const float mn0 = fmaxf(m0, mx0), mn1 = fmaxf(m1, mx1);
         const float ms0 = (mn0 == -INFINITY) ? 0.0f : mn0, ms1 = (mn1 == -INFINITY) ? 0.0f : mn1;
-        const float c0 = (m0 == -INFINITY) ? 0.0f : expf(m0 - ms0);
-        const float c1 = (m1 == -INFINITY) ? 0.0f : expf(m1 - ms1);
+        const float c0 = (m0 == -INFINITY) ? 0.0f : ad_ex2(m0 - ms0);
+        const float c1 = (m1 == -INFINITY) ? 0.0f : ad_ex2(m1 - ms1);
         float rs0 = 0.0f, rs1 = 0.0f;
 #pragma unroll
         for (int nt = 0; nt < 2; ++nt) {
 #pragma unroll
             for (int i = 0; i < 2; ++i) {
-                s[nt][i] = expf(s[nt][i] - ms0);
-                s[nt][2 + i] = expf(s[nt][2 + i] - ms1);
+                s[nt][i] = ad_ex2(s[nt][i] - ms0);
+                s[nt][2 + i] = ad_ex2(s[nt][2 + i] - ms1);
                 rs0 += s[nt][i];
                 rs1 += s[nt][2 + i];
             }
         }
-        rs0 += __shfl_xor_sync(0xffffffffu, rs0, 1);
-        rs0 += __shfl_xor_sync(0xffffffffu, rs0, 2);
-        rs1 += __shfl_xor_sync(0xffffffffu, rs1, 1);
-        rs1 += __shfl_xor_sync(0xffffffffu, rs1, 2);
+        // the sums stay per lane (four lanes share a row); they are put together once, after
+        // the last page
         l0 = l0 * c0 + rs0;
         l1 = l1 * c1 + rs1;
         m0 = mn0;
@@ -213,6 +228,10 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
         if (tid == 0 && it + AD_STAGES < npages) issue(stage, pg_a + it + AD_STAGES);
     }
 
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
+    l0 += __shfl_xor_sync(0xffffffffu, l0, 2);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 1);
+    l1 += __shfl_xor_sync(0xffffffffu, l1, 2);
     // Merge the four warps through shared memory (all stages have been consumed).
     float* so = reinterpret_cast<float*>(smem);   // [4][G][D]
     if (t == 0) {
@@ -243,7 +262,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
 #pragma unroll
         for (int w = 0; w < 4; ++w) {
             const float mw = s_m[w][row];
-            const float f = (mw == -INFINITY) ? 0.0f : expf(mw - M);
+            const float f = (mw == -INFINITY) ? 0.0f : ad_ex2(mw - M);
             const float4 v = *reinterpret_cast<const float4*>(so + ((size_t)(w * G + row)) * D + e);
             acc.x += v.x * f; acc.y += v.y * f; acc.z += v.z * f; acc.w += v.w * f;
             l += s_l[w][row] * f;
@@ -290,7 +309,7 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             const float2 ml = __ldcg(reinterpret_cast<const float2*>(part_ml + (base + cc) * 2));
             const float4 v = __ldcg(reinterpret_cast<const float4*>(part_o + (base + cc) * D + e));
             const float mn = fmaxf(M, ml.x);
-            const float a = expf(M - mn), f = expf(ml.x - mn);   // a = 0 at the first segment
+            const float a = ad_ex2(M - mn), f = ad_ex2(ml.x - mn);   // a = 0 at the first segment
             acc.x = acc.x * a + v.x * f; acc.y = acc.y * a + v.y * f;
             acc.z = acc.z * a + v.z * f; acc.w = acc.w * a + v.w * f;
             L = L * a + ml.y * f;
@@ -320,12 +339,12 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
     float M = -INFINITY;
     for (int c = c0; c <= c1; ++c) M = fmaxf(M, part_ml[(base + c) * 2]);
     float L = 0.0f;
-    for (int c = c0; c <= c1; ++c) L += part_ml[(base + c) * 2 + 1] * expf(part_ml[(base + c) * 2] - M);
+    for (int c = c0; c <= c1; ++c) L += part_ml[(base + c) * 2 + 1] * ad_ex2(part_ml[(base + c) * 2] - M);
     const float inv = 1.0f / L;
     for (int e = threadIdx.x; e < D; e += blockDim.x) {
         float acc = 0.0f;
         for (int c = c0; c <= c1; ++c)
-            acc += part_o[(base + c) * D + e] * expf(part_ml[(base + c) * 2] - M);
+            acc += part_o[(base + c) * D + e] * ad_ex2(part_ml[(base + c) * 2] - M);
         out[((size_t)b * nq + head) * D + e] = from_f32<TOut>(acc * inv);
     }
 }
@@ -361,6 +380,7 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
         if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) sms = 148;
     }
     const bool deep = (long long)max_segs * nkv * B <= 2LL * sms;
+    scale *= 1.4426950408889634f;       // scores in units of log 2 (see ad_ex2)
     auto go = [&](auto kernel, int stages, int dd) -> cudaError_t {
         const int smem = stages * 2 * LUMEN_PAGE * dd * 2;
         cudaError_t err_ = cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, smem);
