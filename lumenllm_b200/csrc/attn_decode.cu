@@ -225,7 +225,20 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             if (tid == 0) atomicExch(err, 1);
             return;
         }
-        if (tid == 0 && it + AD_STAGES < npages) issue(stage, pg_a + it + AD_STAGES);
+        // the refill is issued by two warps, the K copy by one and the V copy by another: a bulk
+        // copy holds its issuing thread some 150 cycles, and the block waits for its slowest warp
+        if (lane == 0 && warp < 2 && it + AD_STAGES < npages) {
+            const int idx = it + AD_STAGES;
+            const int page = idx < AD_PAGE_IDS ? s_page[idx] : bt[pg_a + idx];
+            const size_t off = ((size_t)page * nkv + kvh) * (size_t)(LUMEN_PAGE * D);
+            unsigned char* dst = smem + stage * 2 * TILE_BYTES;
+            if (warp == 0) {
+                mbar_expect_tx(&full[stage], 2 * TILE_BYTES);
+                bulk_load(dst, kcache + off, TILE_BYTES, &full[stage]);
+            } else {
+                bulk_load(dst + TILE_BYTES, vcache + off, TILE_BYTES, &full[stage]);
+            }
+        }
     }
 
     l0 += __shfl_xor_sync(0xffffffffu, l0, 1);
@@ -285,16 +298,20 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     // Merge without a second kernel and without waiting: every block of this (sequence, kv
     // head) counts itself in after its partials are visible; the one that counts last merges
     // all segments, in rising order whoever it is, and puts the counter back to zero.
-    __threadfence();
+    // (the barrier orders every thread's partials before thread 0's release, which is
+    // cumulative; the last block's acquire and its barrier order them before the reads below)
     __syncthreads();
     if (tid == 0) {
-        const int ticket = atomicAdd(&counters[b * nkv + kvh], 1);
+        int ticket;
+        asm volatile("atom.acq_rel.gpu.global.add.s32 %0, [%1], 1;"
+                     : "=r"(ticket)
+                     : "l"(counters + b * nkv + kvh)
+                     : "memory");
         s_last = (ticket == plan.nseg - 1);
         if (s_last) counters[b * nkv + kvh] = 0;
     }
     __syncthreads();
     if (!s_last) return;
-    __threadfence();
     // One pass with a running maximum, so that every load of a thread is in flight at once:
     // a thread owns four values of one head and reads each segment's (m, l) itself.
     const int nch = plan.nseg;
