@@ -33,6 +33,10 @@
 // scores 2,270 cycles, then its O product, then its next S product) leaves the one issuing
 // thread either held by the pipe or waiting, and a step of four page tiles took 4,100 to
 // 4,300 cycles: 650 us at 8,192 tokens against 544 us for this kernel. Taken out again.
+// So was the smaller step of this kernel with the S product taken over pairs of pages (one
+// 128-column product into both S buffers, K tiles interleaved by 64-value block): the same
+// bits, 634 against 544 us, because the next pair's S product cannot be issued before both O
+// products of this pair, and the softmax, never idle here, then waits for it once a pair.
 // O is rescaled only when a row's maximum has grown by more than 2^8 since the reference it
 // was accumulated against (P and the row sum use the same reference, so the result is exact);
 // the rescale is a read-modify-write of the row in tensor memory and is rare after the first
