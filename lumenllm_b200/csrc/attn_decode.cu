@@ -368,7 +368,8 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
 
 // Entry point. q, out: bfloat16 [B, nq, D]; caches in the swizzled layout; seq_pos[b] is the
 // position of sequence b's query (its cached length before this token). seg_pages: the most
-// pages a segment has, 1 to 8 (small for few sequences, so that there are blocks enough).
+// pages a segment has, 1 to 8 (callers that want a sequence's result to be the same in every
+// batch pass the same number for every batch; the library's own decode step passes 4).
 // max_segs: segments the scratch has room for per (sequence, head): at least
 // min(ceil(bt_stride / seg_pages), 32), the most a sequence is cut into. part_o and part_ml
 // are the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
