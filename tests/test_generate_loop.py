@@ -210,3 +210,22 @@ def test_a_refused_step_gives_the_slots_back(ahead):
     with pytest.raises(RuntimeError, match="exhausted"):
         generate(b, [GenerateRequest([5, 6], max_tokens=8), GenerateRequest([7], max_tokens=8)])
     assert not b.held and sorted(b.free) == list(range(4))
+
+
+def test_the_shape_of_a_captured_step_depends_on_counts_alone():
+    """Which captured step serves a batch: tokens and sequences rounded up to buckets, the
+    surplus tokens in the first padding sequence, the other padding sequences empty; a step of
+    one token each has as many tokens as sequences."""
+    from lumenllm_b200.engine.step_graph import StepGraphs
+    assert StepGraphs.plan([1]) == (1, 1, [])
+    assert StepGraphs.plan([1, 1, 1]) == (4, 4, [1])
+    assert StepGraphs.plan([1] * 9) == (16, 16, [1] * 7)
+    assert StepGraphs.plan([1] * 65) == (128, 128, [1] * 63)
+    assert StepGraphs.plan([128]) == (128, 2, [0])                  # a full bucket needs no padding token
+    assert StepGraphs.plan([33, 2, 65]) == (128, 4, [28])
+    assert StepGraphs.plan([70, 20, 7]) == (128, 4, [31])           # another division, the same shape
+    assert StepGraphs.plan([100, 1]) == (128, 4, [27, 0])
+    assert StepGraphs.plan([513]) == (576, 2, [63])
+    for lens in ([5], [1, 2], [600, 300], [31] * 7):
+        n_tok, n_seq, pads = StepGraphs.plan(lens)
+        assert n_tok == sum(lens) + sum(pads) and n_seq == len(lens) + len(pads) and n_tok > n_seq
