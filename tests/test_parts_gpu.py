@@ -1,8 +1,9 @@
 """Each part of a layer alone against its plain formula, and the generality of the
 composition: a layer named twice in the schedule, a layer that reads another layer's cache,
 and toy parts (a mixer with per-sequence state of its own, a feed-forward with routing, a
-position encoding with other frequencies and positions) that are registered here, in the test,
-and built and stepped without a change to the library."""
+position encoding with other frequencies and positions, another norm and another arrangement
+of a block) that are registered here, in the test, and built and stepped without a change to
+the library."""
 from dataclasses import replace
 
 import pytest
@@ -570,4 +571,100 @@ def test_a_toy_position_encoding(dtype, tiny_models):
     got = _step_whole_tail_and_batch(eng, seqs, [30, 2, 20])
     for a, r in zip(got, refs):
         assert float((a - r).abs().max()) < tolerance(name, r)
+    eng.cache.check()
+
+
+@pytest.mark.parametrize("dtype", [F32, BF16])
+def test_a_toy_block_arrangement_and_a_toy_norm(dtype, tiny_models):
+    """Another arrangement of a layer's parts, registered here: the mixer and the feed-forward
+    both read ONE norm of the stream and their updates are added side by side
+    (h' = h + mixer(n(h)) + ffn(n(h))), with a norm of its own kind (a root-mean-square norm
+    whose weight is 1 + w, built on the library's norm kernel through its weight_offset). The
+    block hands both updates on as one stack of partial sums for the next norm to add. Layer 1
+    of model B is arranged this way, layers 0 and 2 keep the library's; stepped whole, token
+    by token (through the captured step) and in a batch."""
+    from lumenllm_b200 import Engine
+    from lumenllm_b200.config import PartSpec
+    from lumenllm_b200.ops import kernels as K
+    from lumenllm_b200.parts import build_part, part_tensors, register_part
+
+    @register_part("norm", "toy_one_plus_weight")
+    class OnePlusWeight:
+        @classmethod
+        def tensors(cls, spec):
+            return {f"{spec.prefix}.weight": ((spec.params["size"],), "norm")}
+
+        def __init__(self, spec, weights, runtime):
+            self.eps = float(spec.params["eps"])
+            self.weight = (weights[f"{spec.prefix}.weight"].to(device=runtime.device, dtype=torch.float32) + 1.0).contiguous()
+
+        def forward(self, h, delta, out_dtype, rows=None, write_h=True):
+            return K.add_rmsnorm(h, delta, self.weight, self.eps, out_dtype, rows=rows, write_h=write_h)
+
+    @register_part("block", "toy_parallel")
+    class Parallel:
+        @classmethod
+        def tensors(cls, layer_spec):
+            t = {}
+            t.update(part_tensors("norm", layer_spec.norms["both"]))
+            t.update(part_tensors("mixer", layer_spec.mixer))
+            t.update(part_tensors("ffn", layer_spec.ffn))
+            return t
+
+        def __init__(self, layer_spec, weights, runtime):
+            self.runtime = runtime
+            self.norm = build_part("norm", layer_spec.norms["both"], weights, runtime)
+            self.mixer = build_part("mixer", layer_spec.mixer, weights, runtime)
+            self.ffn = build_part("ffn", layer_spec.ffn, weights, runtime)
+
+        def forward(self, h, pending, ctx, entry):
+            y = self.norm.forward(h, pending, self.runtime.dtype)
+            a = self.mixer.forward(y, ctx, entry)
+            m = self.ffn.forward(y, ctx)
+            stack = lambda u: u if u.dim() == 3 else u.unsqueeze(0)
+            return h, torch.cat([stack(a), stack(m)], dim=0).contiguous()
+
+    cfg = TINY["B"]
+    base = spec_of("B")
+    layers = list(base.layers)
+    toy_norm = PartSpec("toy_one_plus_weight", {"size": 96, "eps": 1e-5}, prefix="model.layers.1.input_layernorm")
+    layers[1] = replace(layers[1], block="toy_parallel", norms={"both": toy_norm})
+    spec = replace(base, layers=tuple(layers))
+    w = gpu_weights(tiny_models["B"])
+    del w["model.layers.1.post_attention_layernorm.weight"]          # the arrangement has one norm
+    wf = {k: v.float().cpu() for k, v in w.items()}
+    name = "float32" if dtype == F32 else "bfloat16"
+    eng = Engine(spec, w, dtype=name, max_tokens=2048)
+    assert eng.model.graph_safe
+
+    def plain(tokens):
+        tokens = torch.tensor(tokens)
+        pos = torch.arange(len(tokens))
+        h = P.embed(tokens, wf["model.embed_tokens.weight"])
+        for i in range(3):
+            if i != 1:
+                h = P.decoder_layer(h, wf, i, cfg, pos)
+                continue
+            p = "model.layers.1."
+            y = P.rms_norm(h, wf[p + "input_layernorm.weight"] + 1.0, 1e-5)
+            h = h + P.attention_block(y, wf, p, cfg, pos, 0) + P.mlp_block(y, wf, p)
+        return P.rms_norm(h, wf["model.norm.weight"], 1e-5) @ wf["lm_head.weight"].T
+
+    seqs = seeded_tokens(384, [40, 3, 21], 9)
+    refs = [plain(q) for q in seqs]
+    got = _step_whole_tail_and_batch(eng, seqs, [30, 1, 21])
+    for g, r in zip(got, refs):
+        assert float((g - r).abs().max()) < tolerance(name, r)
+    # and single tokens through the captured step
+    from lumenllm_b200 import StepEntry
+    from lumenllm_b200.sampling import SamplingConfig
+    slots = [eng.alloc_slot() for _ in range(2)]
+    eng.step([StepEntry(s, q[:10], []) for s, q in zip(slots, (seqs[0], seqs[2]))])
+    for t in range(10, 14):
+        eng.run_device([(slots[0], [seqs[0][t]]), (slots[1], [seqs[2][t]])], [SamplingConfig()] * 2, [0.0] * 2)
+        lg = eng.graphs.last.logits[:2].float().cpu()
+        for k, r in enumerate((refs[0], refs[2])):
+            assert float((lg[k] - r[t]).abs().max()) < tolerance(name, r), (t, k)
+    for s in slots:
+        eng.free_slot(s)
     eng.cache.check()
