@@ -67,6 +67,43 @@ LUMEN_API int lumen_embed(const int* tokens, const void* table, int table_is_bf1
     return 0;
 }
 
+// The same from a table kept in the tiled form of the tensor-core products (the head of
+// csrc/gemm_tc.cu describes it): when the output head shares the embedding's matrix there is
+// one copy of it, in the form the product reads. Piece c (8 values) of row r lies in k block
+// c / 8 at row kb * w_rows + r, place (c & 7) ^ (r & 7).
+__global__ void embed_tiled_kernel(const int* __restrict__ tokens, const uint4* __restrict__ table,
+                                   float* __restrict__ h, int H, int V, int w_rows) {
+    pdl_wait();      // nothing of this kernel touches global memory before this
+    pdl_trigger();
+    const int t = blockIdx.x;
+    const int tok = tokens[t];
+    float* out = h + (size_t)t * H;
+    const bool ok = tok >= 0 && tok < V;
+    for (int c = threadIdx.x; c < H / 8; c += blockDim.x) {
+        float4 lo = make_float4(0.f, 0.f, 0.f, 0.f), hi = lo;
+        if (ok) {
+            const uint4 v = table[((size_t)(c >> 3) * w_rows + tok) * 8 + ((c & 7) ^ (tok & 7))];
+            const __nv_bfloat162* b = reinterpret_cast<const __nv_bfloat162*>(&v);
+            const float2 f0 = __bfloat1622float2(b[0]), f1 = __bfloat1622float2(b[1]);
+            const float2 f2 = __bfloat1622float2(b[2]), f3 = __bfloat1622float2(b[3]);
+            lo = make_float4(f0.x, f0.y, f1.x, f1.y);
+            hi = make_float4(f2.x, f2.y, f3.x, f3.y);
+        }
+        *reinterpret_cast<float4*>(out + 8 * c) = lo;
+        *reinterpret_cast<float4*>(out + 8 * c + 4) = hi;
+    }
+}
+
+LUMEN_API int lumen_embed_tiled(const int* tokens, const void* table, float* h, int N, int H, int V, int w_rows,
+                                cudaStream_t stream) {
+    if (N <= 0) return 0;
+    if (H <= 0 || V <= 0 || (H & 7) || w_rows < V || (w_rows & 7) || ((uintptr_t)table & 15) || ((uintptr_t)h & 15))
+        return LUMEN_ERR_BAD_ARGUMENT;
+    lumen_launch(embed_tiled_kernel, dim3(N), dim3(256), 0, stream, tokens, (const uint4*)table, h, H, V, w_rows);
+    LUMEN_LAUNCH_CHECK();
+    return 0;
+}
+
 // ---------------------------------------------------------------- add + RMSNorm
 // x = h[r] + delta[0][r] + ... + delta[S-1][r] (summed in that order, float32); if write_h the
 // sum is stored back to h[r]; y = x * 1/sqrt(mean(x^2)+eps) * w. With `rows`, block b reads

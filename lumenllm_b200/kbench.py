@@ -100,7 +100,7 @@ def main(argv=None):
     bf = torch.bfloat16
     note = ""
     if a.kernel == "gemm_tc":
-        ws = [(torch.randn(a.n, a.k, device=dev) / math.sqrt(a.k)).to(bf) for _ in range(a.copies)]
+        ws = [K.tile_weight((torch.randn(a.n, a.k, device=dev) / math.sqrt(a.k)).to(bf)) for _ in range(a.copies)]
         x = torch.randn(a.m, a.k, device=dev).to(bf)
         fns = [lambda w=w: K.gemm_tc(x, w, silu_interleaved=a.silu) for w in ws]
         us = _time(fns, a.reps)
@@ -160,7 +160,7 @@ def main(argv=None):
     else:
         # the QKV product of a prompt with norm, rotation and cache write in its epilogue
         nh = a.heads + 2 * a.kv_heads
-        ws = [(torch.randn(nh * 128, a.k, device=dev) / math.sqrt(a.k)).to(bf) for _ in range(a.copies)]
+        ws = [K.tile_weight((torch.randn(nh * 128, a.k, device=dev) / math.sqrt(a.k)).to(bf)) for _ in range(a.copies)]
         x = torch.randn(a.m, a.k, device=dev).to(bf)
         kc, vc, table = _paged(1, a.m, a.kv_heads, 128, dev)
         pos = torch.arange(a.m, dtype=torch.int32, device=dev)

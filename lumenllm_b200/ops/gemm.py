@@ -5,7 +5,8 @@ prompts, a weight-streaming orientation with k split for decode and short prompt
 may come back as S partial sums [S, M, N] for the consumer to add, or be added to the residual
 stream in place. The library product (cuBLAS through torch, as the reference uses cuBLASLt:
 crates/aegisllm-cuda/src/cuda/runtime/cublaslt.rs:57-165) stands only where a row of the
-operands is not a multiple of 16 bytes, which the TMA cannot address.
+operands is not a multiple of 16 bytes, which the TMA cannot address. Weights reach the
+tensor-core kernels in tiled form (kernels.tile_weight), made once when the model is built.
 """
 from __future__ import annotations
 
@@ -19,12 +20,14 @@ torch.backends.cuda.matmul.allow_tf32 = False
 torch.backends.cudnn.allow_tf32 = False
 
 
-def takes_tc(x: torch.Tensor, w: torch.Tensor) -> bool:
-    return x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and w.data_ptr() % 16 == 0
+def takes_tc(x: torch.Tensor, w) -> bool:
+    """A weight in tiled form goes to the tensor-core kernels (it exists only where its rows are
+    multiples of 16 bytes); a plain tensor is a weight they cannot address."""
+    return isinstance(w, K.TiledWeight) and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0
 
 
 def gemm_bf16(x: torch.Tensor, w: torch.Tensor, split_ok: bool = False, add_to=None):
-    """x bfloat16 [M, K], w bfloat16 [N, K] -> float32 [M, N]; with split_ok possibly
+    """x bfloat16 [M, K], w bfloat16 [N, K] (tiled, or a plain tensor) -> float32 [M, N]; with split_ok possibly
     [S, M, N] partial sums that the consumer adds. With add_to (float32 [M, N]) the product
     may instead be added to it in place, where the kernel for this shape can do that; None
     is returned then, and the caller has nothing left to add."""
@@ -40,6 +43,9 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, split_ok: bool = False, add_to=N
             return K.gemm_tc(x, w, add_to=add_to)
         part = K.gemm_tc(x, w)
     else:
+        if isinstance(w, K.TiledWeight):
+            raise KernelError(f"gemm_bf16: activations [{x.shape[0]}, {x.shape[1]}] do not fit a tiled weight "
+                              f"{w.shape} (rows of 16 bytes, 16-byte aligned)")
         return torch.mm(x, w.t(), out_dtype=torch.float32)
     if part.shape[0] == 1:
         return part[0]

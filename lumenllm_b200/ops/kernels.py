@@ -42,10 +42,17 @@ def _partials(t, name):
 
 
 def embed(tokens, table, out=None):
-    """h[t] = float32(table[tokens[t]]). tokens int32 [N]; table [V, H] float32|bfloat16."""
+    """h[t] = float32(table[tokens[t]]). tokens int32 [N]; table [V, H] float32|bfloat16, or
+    a TiledWeight (the table an output head shares)."""
     require(tokens, I32, "embed.tokens")
     N = tokens.numel()
     V, H = table.shape
+    if isinstance(table, TiledWeight):
+        if out is None:
+            out = torch.empty((N, H), dtype=F32, device=table.device)
+        f = fn("core", "lumen_embed_tiled", [P, P, P, c_int, c_int, c_int, c_int, P])
+        check(f(ptr(tokens), ptr(table.data), ptr(out), N, H, V, table.padded_rows, stream_ptr()), "embed")
+        return out
     if not table.is_contiguous() or not table.is_cuda:
         raise KernelError("embed.table must be a contiguous CUDA tensor")
     if out is None:
@@ -155,11 +162,12 @@ def gemm_tc_qkv_takes(M, N, K, nq, nkv, d, rotary_dim) -> bool:
 def gemm_tc_qkv(x, w, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, tok_seq, block_table,
                 kcache, vcache, nq, nkv):
     """The QKV product of a prompt with qk_norm_rope_store folded into its epilogue: x bfloat16
-    [M, K], w bfloat16 [(nq + 2 nkv) * 128, K] (q heads, k heads, v heads); returns q bfloat16
+    [M, K], w a TiledWeight [(nq + 2 nkv) * 128, K] (q heads, k heads, v heads); returns q bfloat16
     [M, nq, 128], normed and rotated, and writes k and v to their places in the swizzled
     bfloat16 cache. Only where gemm_tc_qkv_takes says so."""
     require(x, BF16, "gemm_tc_qkv.x")
-    require(w, BF16, "gemm_tc_qkv.w")
+    if not isinstance(w, TiledWeight):
+        raise KernelError("gemm_tc_qkv takes its weight in tiled form (tile_weight)")
     M, K = x.shape
     N = w.shape[0]
     if w.shape[1] != K or not gemm_tc_qkv_takes(M, N, K, nq, nkv, 128, rotary_dim):
@@ -184,8 +192,8 @@ def gemm_tc_qkv(x, w, q_norm_w, k_norm_w, eps, cs, rotary_dim, cache_pos, tok_se
         raise KernelError(f"gemm_tc_qkv: caches must be [pages, nkv, {PAGE}, 128]")
     q_out = torch.empty((M, nq, 128), dtype=BF16, device=x.device)
     f = fn("gemm_tc", "lumen_gemm_tc_qkv",
-           [P, P, c_int, c_int, c_int, P, P, P, P, P, c_float, P, c_int, P, P, P, c_int, c_int, c_int, P, P])
-    check(f(ptr(x), ptr(w), M, N, K, ptr(q_out), ptr(kcache), ptr(vcache), ptr(q_norm_w), ptr(k_norm_w),
+           [P, P, c_int, c_int, c_int, c_int, P, P, P, P, P, c_float, P, c_int, P, P, P, c_int, c_int, c_int, P, P])
+    check(f(ptr(x), ptr(w.data), M, N, K, w.padded_rows, ptr(q_out), ptr(kcache), ptr(vcache), ptr(q_norm_w), ptr(k_norm_w),
             float(eps), ptr(cs), int(rotary_dim), ptr(cache_pos), ptr(tok_seq), ptr(block_table),
             block_table.stride(0), nq, nkv, ptr(error_flag(x.device)), stream_ptr()), "gemm_tc_qkv")
     return q_out
@@ -229,6 +237,64 @@ def gemm_f32(a, w, out=None):
     return out
 
 
+class TiledWeight:
+    """A bfloat16 weight [rows, cols] in the form the tensor-core products read: the image its
+    tiles have in shared memory, k block after k block, rows padded to `padded_rows` (see the
+    head of csrc/gemm_tc.cu). `first_rows(n)` is the weight's first n rows on the same memory."""
+    __slots__ = ("data", "rows", "cols", "padded_rows")
+
+    def __init__(self, data, rows, cols, padded_rows):
+        self.data, self.rows, self.cols, self.padded_rows = data, int(rows), int(cols), int(padded_rows)
+
+    @property
+    def shape(self):
+        return (self.rows, self.cols)
+
+    @property
+    def dtype(self):
+        return self.data.dtype
+
+    @property
+    def device(self):
+        return self.data.device
+
+    def data_ptr(self):
+        return self.data.data_ptr()
+
+    def first_rows(self, n: int) -> "TiledWeight":
+        if not 0 < n <= self.rows:
+            raise KernelError(f"a tiled weight of {self.rows} rows has no first {n} rows")
+        return TiledWeight(self.data, n, self.cols, self.padded_rows)
+
+    def row_major(self) -> torch.Tensor:
+        """The weight as an ordinary [rows, cols] tensor again (a copy; tests and debugging)."""
+        kb = (self.cols + 63) // 64
+        t = self.data.view(kb, self.padded_rows, 8, 8)                 # [k block, row, piece, 8 values]
+        r = torch.arange(self.padded_rows, device=t.device) % 8
+        j = torch.arange(8, device=t.device)
+        src = (j[None, :] ^ r[:, None])                                # piece c of row r sits at place c ^ (r & 7)
+        t = torch.gather(t, 2, src[None, :, :, None].expand(kb, -1, -1, 8))
+        return t.permute(1, 0, 2, 3).reshape(self.padded_rows, kb * 64)[: self.rows, : self.cols].contiguous()
+
+
+def can_tile(w) -> bool:
+    return (isinstance(w, torch.Tensor) and w.dtype == BF16 and w.is_cuda and w.dim() == 2
+            and w.shape[1] % 8 == 0 and w.shape[0] > 0)
+
+
+def tile_weight(w) -> TiledWeight:
+    """The tiled form of a bfloat16 weight [N, K], K a multiple of 8."""
+    require(w, BF16, "tile_weight.w")
+    if not can_tile(w):
+        raise KernelError(f"tile_weight takes bfloat16 [N, K] with K a multiple of 8, not {tuple(w.shape)}")
+    N, K = w.shape
+    padded = int(int_fn("gemm_tc", "lumen_tiled_weight_rows", [c_int])(int(N)))
+    out = torch.empty(((K + 63) // 64) * padded * 64, dtype=BF16, device=w.device)
+    f = fn("gemm_tc", "lumen_tile_weight", [P, P, c_int, c_int, P])
+    check(f(ptr(w), ptr(out), N, K, stream_ptr()), "tile_weight")
+    return TiledWeight(out, N, K, padded)
+
+
 def gemm_tc_splits(M, N, K, silu=False) -> int:
     return int(int_fn("gemm_tc", "lumen_gemm_tc_splits", [c_int, c_int, c_int, c_int])(
         int(M), int(N), int(K), 1 if silu else 0))
@@ -240,13 +306,14 @@ def gemm_tc_adds(M, N) -> bool:
 
 
 def gemm_tc(x, w, silu_interleaved=False, add_to=None):
-    """x @ w.T on the tcgen05 tensor cores. x bfloat16 [M, K], w bfloat16 [N, K], K a
+    """x @ w.T on the tcgen05 tensor cores. x bfloat16 [M, K], w a TiledWeight [N, K], K a
     multiple of 8. Returns float32 partials [S, M, N] (S = 1 unless M <= 256); or, with
     silu_interleaved (rows of w alternate gate_i, up_i), bfloat16 [M, N/2] = silu(gate)*up;
     or, with add_to (float32 [M, N], only where gemm_tc_adds(M, N)), adds the product to it
     in place (one float32 add an element, by the copy engine) and returns None."""
     require(x, BF16, "gemm_tc.x")
-    require(w, BF16, "gemm_tc.w")
+    if not isinstance(w, TiledWeight):
+        raise KernelError("gemm_tc takes its weight in tiled form (tile_weight)")
     M, K = x.shape
     N, K2 = w.shape
     if K != K2 or K % 8:
@@ -263,8 +330,9 @@ def gemm_tc(x, w, silu_interleaved=False, add_to=None):
         out, epi = torch.empty((M, N // 2), dtype=BF16, device=x.device), 1
     else:
         out = torch.empty((gemm_tc_splits(M, N, K), M, N), dtype=F32, device=x.device)
-    f = fn("gemm_tc", "lumen_gemm_tc", [P, P, P, c_int, c_int, c_int, c_int, P, P])
-    check(f(ptr(x), ptr(w), ptr(out), M, N, K, epi, ptr(error_flag(x.device)), stream_ptr()), "gemm_tc")
+    f = fn("gemm_tc", "lumen_gemm_tc", [P, P, P, c_int, c_int, c_int, c_int, c_int, P, P])
+    check(f(ptr(x), ptr(w.data), ptr(out), M, N, K, w.padded_rows, epi, ptr(error_flag(x.device)), stream_ptr()),
+          "gemm_tc")
     return None if add_to is not None else out
 
 

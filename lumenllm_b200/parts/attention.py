@@ -59,8 +59,7 @@ class GQAttention:
             mats += [weights[f"{pre}.k_proj.weight"], weights[f"{pre}.v_proj.weight"]]
         self.qkv = Linear.stacked(mats, runtime)
         # a run that reads another run's cache projects queries only
-        self.q_only = self.qkv if self.shares_cache else \
-            Linear(self.qkv.weight[: self.nq * self.d], runtime)
+        self.q_only = self.qkv if self.shares_cache else self.qkv.first_rows(self.nq * self.d)
         self.o = Linear(weights[f"{pre}.o_proj.weight"], runtime)
         self.q_norm = self.k_norm = None
         self.qk_eps = float(p.get("qk_norm_eps", 0.0))

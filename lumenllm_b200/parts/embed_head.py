@@ -9,7 +9,7 @@ from __future__ import annotations
 
 from ..ops import kernels as K
 from .base import need, register_part
-from .linear import Linear
+from .linear import Linear, tiled_form
 
 
 @register_part("embedding", "token_embedding")
@@ -23,6 +23,10 @@ class TokenEmbedding:
     def __init__(self, spec, weights, runtime):
         self.table = weights[f"{spec.prefix}.weight"].contiguous()
         self.vocab_size = self.table.shape[0]
+        # in a bfloat16 run the table is kept in the form an output head would read it in, so
+        # that a head tied to it shares the one copy
+        if not runtime.is_f32 and K.can_tile(self.table):
+            self.table = tiled_form(self.table)
         self.scale = spec.params.get("scale")
 
     def forward(self, tokens):

@@ -424,13 +424,13 @@ def test_gemm_tc_tensor_memory_product(M, N, K_):
     g = gen(16)
     x = torch.randn(M, K_, generator=g).to(BF16)
     w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(BF16)
-    part = K.gemm_tc(dev(x), dev(w)).cpu()
+    part = K.gemm_tc(dev(x), K.tile_weight(dev(w))).cpu()
     K.check_error_flags()
     assert part.shape == (K.gemm_tc_splits(M, N, K_), M, N)
     ref = x.double() @ w.double().T
     assert float((part.sum(0).double() - ref).abs().max()) < 1e-4
     if M <= 16:        # the same row alone: same tile shape, same order of sums
-        one = K.gemm_tc(dev(x[M // 2:M // 2 + 1].contiguous()), dev(w)).cpu()
+        one = K.gemm_tc(dev(x[M // 2:M // 2 + 1].contiguous()), K.tile_weight(dev(w))).cpu()
         assert torch.equal(one[:, 0], part[:, M // 2])
 
 
@@ -445,22 +445,54 @@ def test_gemm_tc_two_sm_product(M, N, K_):
     w = (torch.randn(N, K_, generator=g) / math.sqrt(K_)).to(BF16)
     w[7] *= 30.0                      # a row and a column that stand out show a misplaced tile
     x[M - 3] *= 20.0
-    out = K.gemm_tc(dev(x), dev(w)).cpu()
+    out = K.gemm_tc(dev(x), K.tile_weight(dev(w))).cpu()
     K.check_error_flags()
     assert out.shape == (1, M, N)
     ref = x.double() @ w.double().T
     assert float((out[0].double() - ref).abs().max()) < 1e-4 * max(1.0, float(ref.abs().max()))
     more = torch.cat([x, torch.randn(300, K_, generator=g).to(BF16)])
-    out2 = K.gemm_tc(dev(more), dev(w)).cpu()
+    out2 = K.gemm_tc(dev(more), K.tile_weight(dev(w))).cpu()
     assert torch.equal(out2[0, :M], out[0])
     # added in place to a float32 matrix (the residual stream): one add an element, exactly
     # what adding the product afterwards gives
     if K.gemm_tc_adds(M, N):
         h = torch.randn(M, N, generator=g)
         hd = dev(h.clone())
-        assert K.gemm_tc(dev(x), dev(w), add_to=hd) is None
+        assert K.gemm_tc(dev(x), K.tile_weight(dev(w)), add_to=hd) is None
         K.check_error_flags()
         assert torch.equal(hd.cpu(), h + out[0])
+
+
+@pytest.mark.parametrize("N,K_", [(1, 8), (130, 72), (256, 64), (700, 200), (4100, 1032)])
+def test_tiled_form_of_a_weight(N, K_):
+    """The form the products read weights in, against its definition: k block after k block,
+    rows padded to a multiple of 256, the 16-byte pieces of row r at the places (piece ^ (r & 7));
+    zeros in the padding; back to rows; the first rows of a weight on the same memory; and an
+    embedding table read from it."""
+    from lumenllm_b200.ops import kernels as K
+    g = gen(31)
+    w = torch.randn(N, K_, generator=g).to(BF16)
+    t = K.tile_weight(dev(w))
+    KB, NP = (K_ + 63) // 64, (N + 255) // 256 * 256
+    assert (t.rows, t.cols, t.padded_rows) == (N, K_, NP) and t.data.numel() == KB * NP * 64
+    padded = torch.zeros(NP, KB * 64, dtype=BF16)
+    padded[:N, :K_] = w
+    want = torch.empty(KB, NP, 8, 8, dtype=BF16)
+    for r8 in range(8):
+        rows = padded[r8::8].view(-1, KB, 8, 8)                       # [row group, k block, piece, 8]
+        for piece in range(8):
+            want[:, r8::8, piece ^ r8] = rows[:, :, piece].permute(1, 0, 2)
+    assert torch.equal(t.data.cpu().view(KB, NP, 8, 8), want)
+    assert torch.equal(t.row_major().cpu(), w)
+    n = max(1, N // 3)
+    assert torch.equal(t.first_rows(n).row_major().cpu(), w[:n])
+    tokens = torch.tensor([0, N - 1, N // 2, N, -1], dtype=I32)
+    got = K.embed(dev(tokens), t).cpu()
+    assert torch.equal(got[:3], w[[0, N - 1, N // 2]].float()) and float(got[3:].abs().max()) == 0.0
+    x = torch.randn(5, K_, generator=g).to(BF16)
+    part = K.gemm_tc(dev(x), t.first_rows(n)).cpu()
+    K.check_error_flags()
+    assert float((part.sum(0).double() - x.double() @ w[:n].double().T).abs().max()) < 1e-3
 
 
 @pytest.mark.parametrize("M,I,H", [(300, 176, 80), (2048, 1536, 256), (40, 176, 80), (3, 12288, 128),
@@ -472,13 +504,13 @@ def test_gemm_tc_with_silu_epilogue_on_interleaved_rows(M, I, H):
     wg = (torch.randn(I, H, generator=g) / math.sqrt(H)).to(BF16)
     wu = (torch.randn(I, H, generator=g) / math.sqrt(H)).to(BF16)
     w = torch.stack([wg, wu], dim=1).reshape(2 * I, H)
-    z = K.gemm_tc(dev(x), dev(w), silu_interleaved=True).cpu().float()
+    z = K.gemm_tc(dev(x), K.tile_weight(dev(w)), silu_interleaved=True).cpu().float()
     K.check_error_flags()
     ref = P.swiglu(x.float() @ wg.float().T, x.float() @ wu.float().T)
     assert z.shape == (M, I)
     assert float(((z - ref).abs() / (1 + ref.abs())).max()) < 2 ** -7
     # the same through the float32 product and the activation kernel
-    gu = K.gemm_tc(dev(x), dev(w))
+    gu = K.gemm_tc(dev(x), K.tile_weight(dev(w)))
     z2 = K.silu_mul(gu, BF16, interleaved=True).cpu().float()
     assert float(((z2 - ref).abs() / (1 + ref.abs())).max()) < 2 ** -7
 
@@ -617,6 +649,7 @@ def test_products_of_drawn_shapes_through_the_router():
     no multiple of 16 bytes): all against the double-precision product."""
     import random
     from lumenllm_b200.ops import gemm as G
+    from lumenllm_b200.ops import kernels as K
     rng = random.Random(7)
     g = gen(51)
     shapes = []
@@ -630,7 +663,8 @@ def test_products_of_drawn_shapes_through_the_router():
     for M, N, Kd in shapes:
         x = torch.randn(M, Kd, generator=g).to(BF16)
         w = (torch.randn(N, Kd, generator=g) / math.sqrt(Kd)).to(BF16)
-        out = G.gemm_bf16(dev(x), dev(w)).cpu()
+        wd = dev(w)
+        out = G.gemm_bf16(dev(x), K.tile_weight(wd) if K.can_tile(wd) else wd).cpu()   # as parts.Linear holds it
         ref = x.double() @ w.double().T
         err = float((out.double() - ref).abs().max())
         assert out.shape == (M, N) and err < 2e-4 * max(1.0, float(ref.abs().max())), (M, N, Kd, err)
@@ -725,7 +759,7 @@ def test_qkv_product_with_norm_rotation_and_cache_write_in_its_epilogue(nq, nkv,
     kcd, vcd = dev(kc), dev(kc.clone())
     kcd2, vcd2 = dev(kc.clone()), dev(kc.clone())
     cs = K.rope_table(dev(pos), dev(P.rope_inv_freq(d, theta, d))) if rot else None
-    xd, wd = dev(x), dev(w)
+    xd, wd = dev(x), K.tile_weight(dev(w))
     q = K.gemm_tc_qkv(xd, wd, dev(qw), dev(kw), eps, cs, rot, dev(pos), dev(seq), dev(table), kcd, vcd, nq, nkv)
     K.check_error_flags()
     # the separate kernels on the same product
@@ -787,9 +821,10 @@ def test_drawn_qkv_products_with_their_epilogue(seed):
     table = dev(table)
     kc, vc, kc2, vc2 = (dev(torch.zeros(n_pages, nkv, 64, d, dtype=BF16)) for _ in range(4))
     cs = K.rope_table(pos, dev(P.rope_inv_freq(d, 50000.0, d))) if rot else None
-    q = K.gemm_tc_qkv(x, w, qw, kw, 1e-6, cs, rot, pos, seq, table, kc, vc, nq, nkv)
+    wt = K.tile_weight(w)
+    q = K.gemm_tc_qkv(x, wt, qw, kw, 1e-6, cs, rot, pos, seq, table, kc, vc, nq, nkv)
     K.check_error_flags()
-    q2 = K.qk_norm_rope_store(K.gemm_tc(x, w), qw, kw, 1e-6, cs, rot, pos, seq, table, kc2, vc2, nq, nkv, d,
+    q2 = K.qk_norm_rope_store(K.gemm_tc(x, wt), qw, kw, 1e-6, cs, rot, pos, seq, table, kc2, vc2, nq, nkv, d,
                               BF16, layout=K.LAYOUT_SW128)
     rel = lambda a, b: float(((a.float() - b.float()).abs() / (1 + b.float().abs())).max())
     what = (seed, nq, nkv, H, lens, starts, rot, normed)
