@@ -38,15 +38,19 @@ __host__ __device__ __forceinline__ int tile_offset(int layout, int r, int e, in
     return r * d + e;
 }
 
-// Programmatic dependent launch. Every kernel of this library starts with pdl_wait() before it
-// reads or writes global memory that another kernel may touch (only set-up that depends on
-// nothing, and reads of weights, may come first), and then lets the next kernel in the stream
-// start its own set-up early with pdl_trigger(). Launched through lumen_launch with the
-// attribute set, kernels overlap their set-up and first weight loads with the tail of the
-// kernel before; launched without it, both instructions do nothing. It is on
-// (4.11 ms against 4.32 ms a decode step at batch 8 of the 8B shape; the weight-streaming
-// products gain most, 36.6 -> 33.4 us for the gate/up product); lumen_set_pdl(0) turns it off for
-// the module it is called in, which the kernel micro-benchmarks do on request.
+// Programmatic dependent launch. Every kernel of this library calls pdl_wait() before it reads
+// or writes global memory that another kernel may touch (only set-up that depends on nothing,
+// and reads of weights and of cache pages written by earlier steps, may come first), and lets
+// the next kernel in the stream start with pdl_trigger(): the short kernels (norms, rotary,
+// SiLU, embedding) at their very top, the attention kernels after their wait, the
+// weight-streaming product when its last loads are about to be asked for (csrc/gemm_tc.cu,
+// TC_TRIGGER_AHEAD). A kernel that was started early still waits for the kernel before it,
+// which waited for the one before that, so the order of the stream holds for everything behind
+// the waits. Launched through lumen_launch with the attribute set, a kernel's set-up and first
+// weight loads run under the tail of the kernels before; launched without it, both
+// instructions do nothing. It is on (3.30 ms a decode step at batch 8 of the 8B shape against
+// 3.55 with every trigger right behind the wait, and 3.8 without); lumen_set_pdl(0) turns it off
+// for the module it is called in, which the kernel micro-benchmarks do on request.
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 

@@ -38,8 +38,8 @@ __device__ __forceinline__ float4 load4(const __nv_bfloat16* p) {
 template <typename TW>
 __global__ void embed_kernel(const int* __restrict__ tokens, const TW* __restrict__ table,
                              float* __restrict__ h, int H, int V) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing of this kernel touches global memory before this
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* out = h + (size_t)t * H;
@@ -73,8 +73,8 @@ LUMEN_API int lumen_embed(const int* tokens, const void* table, int table_is_bf1
 // c / 8 at row kb * w_rows + r, place (c & 7) ^ (r & 7).
 __global__ void embed_tiled_kernel(const int* __restrict__ tokens, const uint4* __restrict__ table,
                                    float* __restrict__ h, int H, int V, int w_rows) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing of this kernel touches global memory before this
     const int t = blockIdx.x;
     const int tok = tokens[t];
     float* out = h + (size_t)t * H;
@@ -122,8 +122,8 @@ add_rmsnorm_kernel(float* __restrict__ h, const float* __restrict__ delta, int S
     const bool one_group = (H & 3) == 0 && (int)blockDim.x * 4 >= H;
     float4 g_early = make_float4(0.f, 0.f, 0.f, 0.f);
     if (one_group && (int)threadIdx.x * 4 < H) g_early = load4(w + threadIdx.x * 4);
-    pdl_wait();      // nothing else of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing else of this kernel touches global memory before this
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
     const float* dr = delta + (size_t)r * H;
@@ -199,8 +199,8 @@ add_rmsnorm_cluster_kernel(float* __restrict__ h, const float* __restrict__ delt
     const int i = (rank * (int)blockDim.x + (int)threadIdx.x) * 4;
     const bool mine = i < H;
     const float4 g = mine ? load4(w + i) : make_float4(0.f, 0.f, 0.f, 0.f);
-    pdl_wait();      // nothing else of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing else of this kernel touches global memory before this
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
     const float* dr = delta + (size_t)r * H;
@@ -265,8 +265,8 @@ add_rmsnorm_rows_kernel(float* __restrict__ h, const float* __restrict__ delta, 
     __shared__ float red[32];
     const int b = blockIdx.x;
     float4 x[ARN_GROUPS];
-    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing of this kernel touches global memory before this
     const int r = rows ? rows[b] : b;
     float* hr = h + (size_t)r * H;
     const float* dr = delta + (size_t)r * H;
@@ -373,8 +373,8 @@ LUMEN_API int lumen_add_rmsnorm(float* h, const float* delta, int n_delta, long 
 template <typename TOut>
 __global__ void silu_mul_kernel(const float* __restrict__ gu, int S, size_t split_stride,
                                 TOut* __restrict__ z, long long total, int I, int interleaved) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing of this kernel touches global memory before this
     long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     const long long step = (long long)gridDim.x * blockDim.x;
     if (interleaved && (I & 3) == 0) {
@@ -468,8 +468,8 @@ LUMEN_API int lumen_silu_mul(const float* gu, int n_splits, void* z, int z_is_bf
 // and read by every layer that shares the position encoding.
 __global__ void rope_table_kernel(const int* __restrict__ pos, const float* __restrict__ inv_freq,
                                   float2* __restrict__ cs, int N, int half) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing of this kernel touches global memory before this
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= (long long)N * half) return;
     const int n = (int)(idx / half), i = (int)(idx - (long long)n * half);
@@ -505,8 +505,8 @@ __global__ void qk_norm_rope_store_kernel(const float* __restrict__ qkv, int S, 
                                           const int* __restrict__ block_table, int bt_stride,
                                           T* __restrict__ q_out, T* __restrict__ kcache,
                                           T* __restrict__ vcache, int nq, int nkv, int d, int layout) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing of this kernel touches global memory before this
     extern __shared__ __align__(16) float rowbuf[];  // [warps][d]
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x;
@@ -572,8 +572,8 @@ qk_norm_rope_store_d128_kernel(const float* __restrict__ qkv, int S, size_t spli
                                const int* __restrict__ tok_seq, const int* __restrict__ block_table,
                                int bt_stride, T* __restrict__ q_out, T* __restrict__ kcache,
                                T* __restrict__ vcache, int nq, int nkv, int layout) {
-    pdl_wait();      // nothing of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing of this kernel touches global memory before this
     constexpr int d = 128;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n = blockIdx.x;
@@ -652,8 +652,8 @@ qk_norm_rope_store_d128_rows_kernel(const float* __restrict__ qkv, int S, size_t
     const float4 one = make_float4(1.f, 1.f, 1.f, 1.f);
     const float4 gq_lo = qw ? load4(qw + 4 * li) : one, gq_hi = qw ? load4(qw + 64 + 4 * li) : one;
     const float4 gk_lo = kw ? load4(kw + 4 * li) : one, gk_hi = kw ? load4(kw + 64 + 4 * li) : one;
-    pdl_wait();      // nothing else of this kernel touches global memory before this
     pdl_trigger();
+    pdl_wait();      // nothing else of this kernel touches global memory before this
     if (head0 >= nheads) return;
     float4 lo[QKR_HPW / 2], hi[QKR_HPW / 2];
     const float* src = qkv + ((size_t)n * nheads + head0 + up) * d + 4 * li;

@@ -45,6 +45,16 @@
 #define TC_BM 128
 #define TC_BK 64
 #define TC_THREADS 192
+// The swapped (weight-streaming) product lets what follows it in the stream start when this
+// many stages of a block's loads are still to be asked for (some 4 us before its stream ends).
+// The short kernel behind it (norm, rotary, SiLU) lets ITS dependents go at its very top, so the
+// next product's blocks come to rest beside this one's (a ring of six stages is 108 KB: two
+// fit an SM) and ask for their first weights just as this product's last loads have been asked
+// for: the stream from HBM does not stop between two products of a decode step. Measured at the
+// 8B shape, batch 8 (ms a step): 3.40 with 0 stages ahead, 3.34 with 9, 3.30 with 11 to 15, 3.35
+// with 18, 3.42 from 24 on and with the trigger at the kernel's top; 3.55 with the trigger right
+// after the wait and a ring of ten stages, where the next product starts when this one has left.
+#define TC_TRIGGER_AHEAD 12
 #define TC_EPI_F32 0
 #define TC_EPI_SILU 1
 #define TC_EPI_ADD 2          // float32, added to what the output holds (two-SM kernel only)
@@ -175,10 +185,7 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     // Set-up above depends on nothing. From here on every role waits for the kernels ahead
     // of this one before it touches activations or outputs; the producer first requests
     // weights (below).
-    if (warp != 0) {
-        pdl_wait();
-        pdl_trigger();
-    }
+    if (warp != 0) pdl_wait();
 
     // item -> (tile of A, tile of B, split); tiles of A vary fastest so that blocks working at
     // the same time share their B tile through L2
@@ -220,12 +227,15 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                 advance();
             }
             pdl_wait();
-            pdl_trigger();
             for (int i = 0; i < npre; ++i) {
                 if (SWAP) tma_load_2d(sB + i * B_BYTES, &tmB, pk[i] * TC_BK, pt[i] * bn, &full[i]);
                 else      tma_load_2d(sA + i * A_BYTES, &tmA, pk[i] * TC_BK, pt[i] * TC_BM, &full[i]);
             }
+            const int my_items = blockIdx.x < n_items ? (n_items - 1 - (int)blockIdx.x) / (int)gridDim.x + 1 : 0;
+            const int trigger_at = my_items * p.kb_per_split - TC_TRIGGER_AHEAD;
+            bool triggered = false;
             for (int it = npre; have && !*abort_flag; ++it, advance()) {
+                if (!triggered && it >= trigger_at) { pdl_trigger(); triggered = true; }
                 const int st = it % STAGES, ph = (it / STAGES) & 1;
                 if (!mbar_wait(&empty[st], ph ^ 1)) { *abort_flag = 1; atomicExch(p.err, 1); break; }
                 mbar_expect_tx(&full[st], stage_bytes);
@@ -237,6 +247,8 @@ gemm_tc_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     tma_load_2d(sB + st * B_BYTES, &tmB, 0, kb * p.w_rows + tb * bn, &full[st]);
                 }
             }
+            // every load of this block is asked for: what follows in the stream may start
+            pdl_trigger();
         } else {
             pdl_wait();
         }
@@ -1199,8 +1211,8 @@ LUMEN_API int lumen_gemm_tc(const void* x, const void* W, void* out, int M, int 
         if ((rc = make_map(&ma, W, N, K, TC_BM, w_rows))) return rc;
         if ((rc = make_map(&mb, x, M, K, bn))) return rc;
         if (epi == TC_EPI_F32) {
-            if (bn == 16) return tc_launch<16, 10, true, TC_EPI_F32>(ma, mb, p, stream);
-            if (bn == 32) return tc_launch<32, 9, true, TC_EPI_F32>(ma, mb, p, stream);
+            if (bn == 16) return tc_launch<16, 6, true, TC_EPI_F32>(ma, mb, p, stream);
+            if (bn == 32) return tc_launch<32, 5, true, TC_EPI_F32>(ma, mb, p, stream);
             if (bn == 64) return tc_launch<64, 8, true, TC_EPI_F32>(ma, mb, p, stream);
             if (bn == 128) return tc_launch<128, 6, true, TC_EPI_F32>(ma, mb, p, stream);
             return tc_launch<256, 4, true, TC_EPI_F32>(ma, mb, p, stream);
