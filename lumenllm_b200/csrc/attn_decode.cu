@@ -25,9 +25,19 @@
 // before it waits for that kernel (programmatic dependent launch); the newest page and the
 // query come after the wait.
 //
+// The kernel can also do the work of the rotary kernel that otherwise stands before it
+// (lumen_attn_decode_qkv, head size 128): then it is given the QKV projection as the product
+// left it, float32 partial sums, and every block makes the query heads of its group itself
+// (sum of the parts, head norm, rotation; qk_head.cuh, the rotary kernel's own arithmetic) into
+// shared memory; the block of a sequence's last segment also makes the new token's key and
+// value, stores them in the cache for the steps to come, and puts them into its own copy of the
+// page once that has arrived. One kernel, and one wait for a kernel ahead, fewer on the step's
+// path; the first pages are requested before the wait as ever.
+//
 // Scratch: part_o [B, nq, max_segs, D] and part_ml [B, nq, max_segs, 2] float32.
 #include "common.cuh"
 #include "mma_utils.cuh"
+#include "qk_head.cuh"
 
 #define AD_THREADS 128
 #define AD_SEG_PAGES 8            // the largest seg_pages a caller may ask for
@@ -65,6 +75,21 @@ __device__ __forceinline__ float ad_ex2(float x) {
     return y;
 }
 
+// What the kernel needs to make q (and the newest k, v) itself; qkv == nullptr: q is given.
+struct AdQkv {
+    const float* qkv;          // [S][B][(nq + 2 nkv) * 128] partial sums of the projection
+    int S;
+    size_t split_stride;
+    const float* qw;           // head norms' weights [128] or null
+    const float* kw;
+    float eps;
+    const float2* cs;          // (cos, sin) [B][64]
+    int rotate;                // whether q and k are rotated
+    int store_kv;              // whether this run owns its cache: make and store the new k, v
+    __nv_bfloat16* kcache;     // the same caches, to write
+    __nv_bfloat16* vcache;
+};
+
 template <int D, int AD_STAGES>
 __global__ void __launch_bounds__(AD_THREADS)
 attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __restrict__ kcache,
@@ -72,8 +97,9 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
                    int bt_stride, const int* __restrict__ seq_pos, float* __restrict__ part_o,
                    float* __restrict__ part_ml, int nq, int nkv, int window, float scale,
                    int max_segs, int seg_pages, int* __restrict__ err, int* __restrict__ counters,
-                   __nv_bfloat16* __restrict__ out) {
+                   __nv_bfloat16* __restrict__ out, const AdQkv f) {
     constexpr int TILE_BYTES = LUMEN_PAGE * D * 2;
+    __shared__ __align__(16) __nv_bfloat16 s_q[16 * D];     // the group's query heads, when made here
     extern __shared__ __align__(1024) unsigned char smem[];   // [stages][K tile, V tile]
     __shared__ uint64_t full[AD_STAGES];
     __shared__ float s_m[4][16], s_l[4][16];
@@ -111,9 +137,14 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     };
     // The first pages of the ring, as far as they are older than this step; then wait for the
     // kernel ahead (it writes the newest token's key and value, and the query), then the rest.
+    // (When this kernel itself makes the new key and value, nobody else writes the newest page
+    // in this step, and it may come early too.)
+    const bool makes_q = D == 128 && f.qkv != nullptr;
+    const bool makes_kv = makes_q && f.store_kv != 0 && seg == plan.nseg - 1;
     int issued = 0;
     if (tid == 0)
-        while (issued < AD_STAGES && issued < npages && pg_a + issued != pg_hi) {
+        while (issued < AD_STAGES && issued < npages &&
+               (pg_a + issued != pg_hi || (makes_q && f.store_kv != 0))) {
             issue(issued, pg_a + issued);
             ++issued;
         }
@@ -125,10 +156,40 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
             ++issued;
         }
 
+    // The group's query heads, a warp a head, into shared memory; warps 2 and 3 of the last
+    // segment's block then make the new token's key and value (4 values a lane, kept for the
+    // block's copy of the page) and store them in the cache.
+    uint2 kv_new = make_uint2(0u, 0u);
+    if (makes_q) {
+        const int nheads = nq + 2 * nkv;
+        const float* tok = f.qkv + (size_t)b * nheads * 128;
+        const float2* cs_b = f.cs + (size_t)b * 64;
+        for (int hh = warp; hh < G; hh += 4) {
+            const float4 v = qk_head_d128(tok + (size_t)(kvh * G + hh) * 128, f.S, f.split_stride, f.qw, f.eps, cs_b,
+                                          f.rotate != 0, lane);
+            uint2 w;
+            w.x = pack_bf16(v.x, v.y);
+            w.y = pack_bf16(v.z, v.w);
+            *reinterpret_cast<uint2*>(s_q + hh * 128 + 4 * lane) = w;
+        }
+        if (makes_kv && warp >= 2) {
+            const bool is_k = warp == 2;
+            const float4 v = qk_head_d128(tok + (size_t)(nq + (is_k ? 0 : nkv) + kvh) * 128, f.S, f.split_stride,
+                                          is_k ? f.kw : nullptr, f.eps, cs_b, is_k && f.rotate != 0, lane);
+            kv_new.x = pack_bf16(v.x, v.y);
+            kv_new.y = pack_bf16(v.z, v.w);
+            const int idx = pg_hi - pg_a;
+            const int page = idx < AD_PAGE_IDS ? s_page[idx] : bt[pg_hi];
+            __nv_bfloat16* tile = (is_k ? f.kcache : f.vcache) + ((size_t)page * nkv + kvh) * (size_t)(LUMEN_PAGE * 128);
+            *reinterpret_cast<uint2*>(tile + tile_offset(LUMEN_LAYOUT_SW128, p % LUMEN_PAGE, 4 * lane, 128)) = kv_new;
+        }
+        __syncthreads();
+    }
+
     // Query fragments: rows = the G heads of this kv head (zero beyond G).
     uint32_t qa[D / 16][4];
     {
-        const __nv_bfloat16* q0 = q + ((size_t)b * nq + (size_t)kvh * G + g) * D;
+        const __nv_bfloat16* q0 = makes_q ? s_q + g * D : q + ((size_t)b * nq + (size_t)kvh * G + g) * D;
         const __nv_bfloat16* q1 = q0 + (size_t)8 * D;
         const bool r0 = g < G, r1 = g + 8 < G;
 #pragma unroll
@@ -151,6 +212,13 @@ attn_decode_kernel(const __nv_bfloat16* __restrict__ q, const __nv_bfloat16* __r
     for (int it = 0; it < npages; ++it) {
         const int stage = it % AD_STAGES;
         if (!mbar_wait(&full[stage], (it / AD_STAGES) & 1)) failed = true;
+        if (makes_kv && it == npages - 1) {
+            // the newest page as it arrived lacks this step's row: put it in
+            if (warp >= 2)
+                *reinterpret_cast<uint2*>(smem + stage * 2 * TILE_BYTES + (warp == 2 ? 0 : TILE_BYTES) +
+                                          2 * tile_offset(LUMEN_LAYOUT_SW128, p % LUMEN_PAGE, 4 * lane, D)) = kv_new;
+            __syncthreads();
+        }
         const uint32_t ktile = smem_u32(smem + stage * 2 * TILE_BYTES);
         const uint32_t vtile = ktile + TILE_BYTES;
 
@@ -366,20 +434,12 @@ __global__ void attn_decode_combine_kernel(const float* __restrict__ part_o,
     }
 }
 
-// Entry point. q, out: bfloat16 [B, nq, D]; caches in the swizzled layout; seq_pos[b] is the
-// position of sequence b's query (its cached length before this token). seg_pages: the most
-// pages a segment has, 1 to 8 (callers that want a sequence's result to be the same in every
-// batch pass the same number for every batch; the library's own decode step passes 4).
-// max_segs: segments the scratch has room for per (sequence, head): at least
-// min(ceil(bt_stride / seg_pages), 32), the most a sequence is cut into. part_o and part_ml
-// are the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
-// counters: null (a second kernel merges the segments), or B * nkv ints that are zero before
-// the call and zero again after it (the last block of each group merges).
-LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* vcache,
-                                const int* block_table, int bt_stride, const int* seq_pos,
-                                void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
-                                int d, int window, float scale, int max_segs, int seg_pages,
-                                int* err, int* counters, cudaStream_t stream) {
+// Checks and launch of both entry points below.
+static int attn_decode_launch(const void* q, const void* kcache, const void* vcache,
+                              const int* block_table, int bt_stride, const int* seq_pos,
+                              void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
+                              int d, int window, float scale, int max_segs, int seg_pages,
+                              int* err, int* counters, cudaStream_t stream, const AdQkv& f) {
     if (B <= 0) return 0;
     if (nq <= 0 || nkv <= 0 || nq % nkv != 0 || nq / nkv > 16 || window < 0 || max_segs <= 0)
         return LUMEN_ERR_UNSUPPORTED;
@@ -405,7 +465,7 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
         if (err_ != cudaSuccess) return err_;
         return lumen_launch(kernel, grid, dim3(AD_THREADS), smem, stream, qp, kp, vp, block_table, bt_stride,
                             seq_pos, part_o, part_ml, nq, nkv, window, scale, max_segs, seg_pages, err, counters,
-                            (__nv_bfloat16*)out);
+                            (__nv_bfloat16*)out, f);
     };
     if (d == 128) {
         e = deep ? go(attn_decode_kernel<128, 3>, 3, 128) : go(attn_decode_kernel<128, 2>, 2, 128);
@@ -424,6 +484,56 @@ LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* v
     if (e != cudaSuccess) return (int)e;
     LUMEN_LAUNCH_CHECK();
     return 0;
+}
+
+// Entry point. q, out: bfloat16 [B, nq, D]; caches in the swizzled layout; seq_pos[b] is the
+// position of sequence b's query (its cached length before this token). seg_pages: the most
+// pages a segment has, 1 to 8 (callers that want a sequence's result to be the same in every
+// batch pass the same number for every batch; the library's own decode step passes 4).
+// max_segs: segments the scratch has room for per (sequence, head): at least
+// min(ceil(bt_stride / seg_pages), 32), the most a sequence is cut into. part_o and part_ml
+// are the caller's scratch (sizes above); err is a device int set to 1 if a copy never arrived.
+// counters: null (a second kernel merges the segments), or B * nkv ints that are zero before
+// the call and zero again after it (the last block of each group merges).
+LUMEN_API int lumen_attn_decode(const void* q, const void* kcache, const void* vcache,
+                                const int* block_table, int bt_stride, const int* seq_pos,
+                                void* out, float* part_o, float* part_ml, int B, int nq, int nkv,
+                                int d, int window, float scale, int max_segs, int seg_pages,
+                                int* err, int* counters, cudaStream_t stream) {
+    AdQkv f = {};
+    return attn_decode_launch(q, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml, B, nq, nkv,
+                              d, window, scale, max_segs, seg_pages, err, counters, stream, f);
+}
+
+// The same with the rotary kernel's work done by the attention blocks (head size 128). qkv:
+// float32 [S][B][(nq + 2 nkv) * 128], the projection's partial sums, split_stride values
+// apart; qw, kw: the head norms' weights [128] or null; cs: (cos, sin) [B][64] for rotate != 0;
+// store_kv != 0: the new token's key and value are made and written to kcache / vcache (a run
+// that reads another run's cache passes 0 and finds them there). The other arguments as above.
+LUMEN_API int lumen_attn_decode_qkv(const float* qkv, int S, long long split_stride, const float* qw,
+                                    const float* kw, float eps, const float* cs, int rotate, int store_kv,
+                                    void* kcache, void* vcache, const int* block_table, int bt_stride,
+                                    const int* seq_pos, void* out, float* part_o, float* part_ml, int B,
+                                    int nq, int nkv, int d, int window, float scale, int max_segs,
+                                    int seg_pages, int* err, int* counters, cudaStream_t stream) {
+    if (d != 128) return LUMEN_ERR_UNSUPPORTED;
+    if (!qkv || S < 1 || (S > 1 && split_stride <= 0) || ((uintptr_t)qkv & 15) || ((split_stride * 4) & 15) ||
+        ((uintptr_t)qw & 15) || ((uintptr_t)kw & 15) || (rotate && (!cs || ((uintptr_t)cs & 15))))
+        return LUMEN_ERR_BAD_ARGUMENT;
+    AdQkv f;
+    f.qkv = qkv;
+    f.S = S;
+    f.split_stride = (size_t)split_stride;
+    f.qw = qw;
+    f.kw = kw;
+    f.eps = eps;
+    f.cs = (const float2*)cs;
+    f.rotate = rotate;
+    f.store_kv = store_kv;
+    f.kcache = (__nv_bfloat16*)kcache;
+    f.vcache = (__nv_bfloat16*)vcache;
+    return attn_decode_launch(nullptr, kcache, vcache, block_table, bt_stride, seq_pos, out, part_o, part_ml, B, nq,
+                              nkv, d, window, scale, max_segs, seg_pages, err, counters, stream, f);
 }
 
 // ---------------------------------------------------------------------------------------

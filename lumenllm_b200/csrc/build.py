@@ -26,12 +26,12 @@ CSRC = Path(__file__).resolve().parent
 
 # module -> (sources compiled into it, headers it depends on)
 MODULES = {
-    "core": (["core.cu"], ["common.cuh"]),
+    "core": (["core.cu"], ["common.cuh", "qk_head.cuh"]),
     "gemm_f32": (["gemm_f32.cu"], ["common.cuh"]),
     "gemm_tc": (["gemm_tc.cu"], ["common.cuh", "mma_utils.cuh"]),
     "attn_generic": (["attn_generic.cu"], ["common.cuh"]),
     "sample": (["sample.cu"], ["common.cuh"]),
-    "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "attn_decode_noalloc.h"]),
+    "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "qk_head.cuh", "attn_decode_noalloc.h"]),
     "attn_prefill": (["attn_prefill.cu"], ["common.cuh", "mma_utils.cuh"]),
     "attn_prefill_tc": (["attn_prefill_tc.cu"], ["common.cuh", "mma_utils.cuh"]),
 }

@@ -8,6 +8,7 @@
 // they are added in rising order of S while they are read.
 #include <cooperative_groups.h>
 #include "common.cuh"
+#include "qk_head.cuh"
 
 template <typename T> struct Pack4;
 template <> struct Pack4<float> {
@@ -580,43 +581,11 @@ qk_norm_rope_store_d128_kernel(const float* __restrict__ qkv, int S, size_t spli
     const int head = blockIdx.y * 8 + warp;
     const int nheads = nq + 2 * nkv;
     if (head >= nheads) return;
-    const float* src = qkv + ((size_t)n * nheads + head) * d + 4 * lane;
-    float4 v = load4(src);
-    for (int s0 = 1; s0 < S; s0 += 8) {       // the partial sums' loads go out together, added in rising order
-        float4 v2[8];
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (s0 + j < S) v2[j] = load4(src + (size_t)(s0 + j) * split_stride);
-#pragma unroll
-        for (int j = 0; j < 8; ++j)
-            if (s0 + j < S) { v.x += v2[j].x; v.y += v2[j].y; v.z += v2[j].z; v.w += v2[j].w; }
-    }
     const bool is_q = head < nq;
     const bool is_k = !is_q && head < nq + nkv;
-    const float* nw = is_q ? qw : (is_k ? kw : nullptr);
-    if (nw) {
-        float ss = v.x * v.x;
-        ss += v.y * v.y;
-        ss += v.z * v.z;
-        ss += v.w * v.w;
-        ss = warp_sum(ss);
-        const float scale = 1.0f / sqrtf(ss / (float)d + eps);
-        const float4 g = load4(nw + 4 * lane);
-        v.x = v.x * scale * g.x; v.y = v.y * scale * g.y; v.z = v.z * scale * g.z; v.w = v.w * scale * g.w;
-    }
-    if ((is_q || is_k) && rot == d) {
-        const float4 o = make_float4(__shfl_xor_sync(0xffffffffu, v.x, 16), __shfl_xor_sync(0xffffffffu, v.y, 16),
-                                     __shfl_xor_sync(0xffffffffu, v.z, 16), __shfl_xor_sync(0xffffffffu, v.w, 16));
-        const float4* csn = reinterpret_cast<const float4*>(cs + (size_t)n * 64 + 4 * (lane & 15));
-        const float4 c01 = csn[0], c23 = csn[1];     // (cos, sin) of 4 consecutive pairs
-        if (lane < 16) {     // x'_i = x_i cos - x_{i+64} sin
-            v.x = v.x * c01.x - o.x * c01.y; v.y = v.y * c01.z - o.y * c01.w;
-            v.z = v.z * c23.x - o.z * c23.y; v.w = v.w * c23.z - o.w * c23.w;
-        } else {             // x'_{i+64} = x_i sin + x_{i+64} cos
-            v.x = o.x * c01.y + v.x * c01.x; v.y = o.y * c01.w + v.y * c01.z;
-            v.z = o.z * c23.y + v.z * c23.x; v.w = o.w * c23.w + v.w * c23.z;
-        }
-    }
+    const float4 v = qk_head_d128(qkv + ((size_t)n * nheads + head) * d, S, split_stride,
+                                  is_q ? qw : (is_k ? kw : nullptr), eps, cs + (size_t)n * 64,
+                                  (is_q || is_k) && rot == d, lane);
     if (is_q) {
         Pack4<T>::store(q_out + ((size_t)n * nq + head) * d + 4 * lane, v.x, v.y, v.z, v.w);
     } else {

@@ -446,6 +446,53 @@ def attn_decode(q, kcache, vcache, block_table, seq_pos, window, scale):
     return out
 
 
+def attn_decode_qkv(qkv, q_norm_w, k_norm_w, eps, cs, rotary_dim, kcache, vcache, block_table, seq_pos,
+                    window, scale, nq, nkv, store_kv=True):
+    """Decode attention that does the rotary kernel's work itself: qkv is the projection as
+    the product left it, float32 [B, (nq + 2 nkv) * 128] or [S, B, ...] partial sums; every
+    block makes its query heads (sum of the parts, head norm with q_norm_w / k_norm_w [128] or
+    None, rotation over the whole head when rotary_dim == 128, by cs [B, 64, 2]), and with
+    store_kv the new token's key and value are made and written to the cache. The same bits as
+    qk_norm_rope_store followed by attn_decode. Head size 128, swizzled bfloat16 cache."""
+    qkv, S = _partials(qkv, "attn_decode_qkv.qkv")
+    B = qkv.shape[1]
+    d = 128
+    if qkv.shape[2] != (nq + 2 * nkv) * d or kcache.shape[1:] != (nkv, PAGE, d) or rotary_dim not in (0, d):
+        raise KernelError(f"attn_decode_qkv: projection {tuple(qkv.shape)} and cache {tuple(kcache.shape)} do not "
+                          f"fit {nq}+2x{nkv} heads of {d} (rotation over {rotary_dim})")
+    require(kcache, BF16, "attn_decode_qkv.kcache")
+    require(vcache, BF16, "attn_decode_qkv.vcache")
+    require(block_table, I32, "attn_decode_qkv.block_table")
+    require(seq_pos, I32, "attn_decode_qkv.seq_pos")
+    for t, nm in ((q_norm_w, "q_norm"), (k_norm_w, "k_norm")):
+        if t is not None:
+            require(t, F32, nm)
+            if t.numel() != d:
+                raise KernelError(f"{nm} weight must have {d} values")
+    if rotary_dim:
+        require(cs, F32, "rope angles")
+        if cs.numel() < B * 64 * 2:
+            raise KernelError("rope angles shorter than the batch")
+    if seq_pos.numel() < B or block_table.shape[0] < B:
+        raise KernelError("attn_decode_qkv: metadata shorter than the batch")
+    width = block_table.shape[1]
+    seg_pages = DECODE_SEG_PAGES
+    max_segs = min(-(-width // seg_pages), DECODE_MAX_SEGS)
+    out = torch.empty((B, nq, d), dtype=BF16, device=qkv.device)
+    part_o = torch.empty((B, nq, max_segs, d), dtype=F32, device=qkv.device)
+    part_ml = torch.empty((B, nq, max_segs, 2), dtype=F32, device=qkv.device)
+    counters = _decode_counters(qkv.device) if B * nkv <= _COUNTERS else None
+    f = fn("attn_decode", "lumen_attn_decode_qkv",
+           [P, c_int, c_longlong, P, P, c_float, P, c_int, c_int, P, P, P, c_int, P, P, P, P, c_int, c_int, c_int,
+            c_int, c_int, c_float, c_int, c_int, P, P, P])
+    check(f(ptr(qkv), S, qkv.stride(0) if S > 1 else 0, ptr(q_norm_w), ptr(k_norm_w), float(eps), ptr(cs),
+            1 if rotary_dim else 0, 1 if store_kv else 0, ptr(kcache), ptr(vcache), ptr(block_table),
+            block_table.stride(0), ptr(seq_pos), ptr(out), ptr(part_o), ptr(part_ml), B, nq, nkv, d, int(window),
+            float(scale), max_segs, seg_pages, ptr(error_flag(qkv.device)), ptr(counters), stream_ptr()),
+          "attn_decode_qkv")
+    return out
+
+
 def attn_prefill(q, kcache, vcache, block_table, cu_q, seq_start, q_lens, window, scale,
                  tensor_memory=True, n_seqs=None):
     """Causal flash attention for sequences that bring q_lens[b] tokens each (host list),

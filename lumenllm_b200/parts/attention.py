@@ -19,6 +19,14 @@ from .base import build_part, need, part_tensors, register_part
 from .linear import Linear
 
 
+# Batches of a decode step for which the attention kernel does the rotary kernel's work itself
+# (ops.kernels.attn_decode_qkv; the same bits either way). It saves a kernel and its wait on the
+# step's path, and costs every block of a sequence's segments the making of its query heads:
+# at the 8B shape 2,455 against 2,424 tokens/s at batch 8 and 4,428 against 4,372 at 16, but
+# 6,985 against 7,083 at 32 and 10,290 against 10,600 at 64; at batch 1 338 against 340.
+FUSED_DECODE_ROWS = (4, 16)
+
+
 @register_part("mixer", "gqa_attention")
 class GQAttention:
     graph_safe = True
@@ -92,6 +100,16 @@ class GQAttention:
             return self.o(out.view(-1, self.nq * self.d), split_ok=True, add_to=residual)
         # float32 [N, (nq + 2 nkv) d], possibly as S partial sums
         qkv = self.qkv(y, split_ok=True) if writes else self.q_only(y, split_ok=True)
+        if (writes and ctx.is_decode and FUSED_DECODE_ROWS[0] <= ctx.B <= FUSED_DECODE_ROWS[1]
+                and entry.layout == K.LAYOUT_SW128 and self.d == 128
+                and self.nq // self.nkv <= 16 and self.position.rotary_dim in (0, 128)
+                and kc.dtype == torch.bfloat16):
+            # one token a sequence, heads of 128: the attention blocks make their query heads and
+            # the new key and value themselves, from the projection's partial sums
+            out = K.attn_decode_qkv(qkv, self.q_norm, self.k_norm, self.qk_eps, self.position.angles(ctx),
+                                    self.position.rotary_dim, kc, vc, table, ctx.cache_pos, self.window,
+                                    self.scale, self.nq, self.nkv)
+            return self.o(out.view(-1, self.nq * self.d), split_ok=True, add_to=residual)
         nkv_new = self.nkv if writes else 0
         q = K.qk_norm_rope_store(qkv, self.q_norm, self.k_norm, self.qk_eps,
                                  self.position.angles(ctx), self.position.rotary_dim,

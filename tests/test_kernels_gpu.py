@@ -344,6 +344,74 @@ def test_attention_decode_of_long_sequences(starts, window):
     assert float((out_g - torch.stack(refs)).abs().max()) < 2 ** -6
 
 
+@pytest.mark.parametrize("nq,nkv,S,rot,normed,window", [(8, 2, 3, 128, True, 0), (4, 4, 1, 128, False, 0),
+                                                         (16, 1, 4, 0, True, 0), (6, 2, 2, 128, True, 90),
+                                                         (32, 8, 3, 128, True, 0)])
+def test_decode_attention_that_makes_its_own_queries(nq, nkv, S, rot, normed, window):
+    """The decode attention given the QKV projection's partial sums instead of finished
+    queries: the same bits, in its output and in the cache, as the rotary kernel followed by the
+    attention kernel. Positions at a page's first and last row, in the first page, far in (so
+    that several segments are merged), sequences of one token; page 0 stays empty. And both
+    against the plain formulas."""
+    from lumenllm_b200.ops import kernels as K
+    d, eps, theta = 128, 1e-5, 30000.0
+    g = gen(71 + nq)
+    starts = [0, 63, 64, 127, 700, 1, 330, 1999][: 8 if nq < 32 else 5]
+    B = len(starts)
+    nh = nq + 2 * nkv
+    parts = torch.randn(S, B, nh * d, generator=g) * (1.0 / math.sqrt(S))
+    qw = dev(1 + 0.1 * torch.randn(d, generator=g)) if normed else None
+    kw = dev(1 + 0.1 * torch.randn(d, generator=g)) if normed else None
+    n_pages = 1 + sum(s // 64 + 1 for s in starts)
+    perm = torch.randperm(n_pages - 1, generator=g) + 1
+    width = max(s // 64 + 1 for s in starts)
+    table = torch.zeros(B, width, dtype=I32)
+    kc = torch.zeros(n_pages, nkv, 64, d, dtype=BF16)
+    vc = torch.zeros_like(kc)
+    o = 0
+    hist = []
+    for b, s in enumerate(starts):
+        np_ = s // 64 + 1
+        pages = perm[o:o + np_]
+        o += np_
+        table[b, :np_] = pages.to(I32)
+        k = torch.randn(np_ * 64, nkv, d, generator=g).to(BF16)
+        v = torch.randn(np_ * 64, nkv, d, generator=g).to(BF16)
+        k[s:] = 0
+        v[s:] = 0                                     # what lies behind a sequence's end is nobody's
+        kc[pages] = k.view(np_, 64, nkv, d).transpose(1, 2)
+        vc[pages] = v.view(np_, 64, nkv, d).transpose(1, 2)
+        hist.append((k[:s].float(), v[:s].float()))
+    pos = dev(torch.tensor(starts, dtype=I32))
+    seq = dev(torch.arange(B, dtype=I32))
+    cs = K.rope_table(pos, dev(P.rope_inv_freq(d, theta, d))) if rot else None
+    kc1, vc1, kc2, vc2 = dev(to_sw128(kc)), dev(to_sw128(vc)), dev(to_sw128(kc)), dev(to_sw128(vc))
+    tab = dev(table)
+    q = K.qk_norm_rope_store(dev(parts), qw, kw, eps, cs, rot, pos, seq, tab, kc1, vc1, nq, nkv, d, BF16,
+                             layout=K.LAYOUT_SW128)
+    out1 = K.attn_decode(q, kc1, vc1, tab, pos, window, d ** -0.5)
+    out2 = K.attn_decode_qkv(dev(parts), qw, kw, eps, cs, rot, kc2, vc2, tab, pos, window, d ** -0.5, nq, nkv)
+    K.check_error_flags()
+    assert torch.equal(out1, out2)
+    assert torch.equal(kc1, kc2) and torch.equal(vc1, vc2)
+    assert float(kc2[0].float().abs().max()) == 0.0 and float(vc2[0].float().abs().max()) == 0.0
+    # the plain formulas: sum of the parts, head norm, rotation, attention over history + the new token
+    x = parts.sum(0).view(B, nh, d)
+    for b, s in enumerate(starts):
+        qh, kh, vh = x[b, :nq], x[b, nq:nq + nkv], x[b, nq + nkv:]
+        if normed:
+            qh = P.rms_norm(qh, qw.cpu(), eps)
+            kh = P.rms_norm(kh, kw.cpu(), eps)
+        if rot:
+            qh = P.apply_rope(qh[None], torch.tensor([s]), theta)[0]
+            kh = P.apply_rope(kh[None], torch.tensor([s]), theta)[0]
+        kh, vh, qh = kh.to(BF16).float(), vh.to(BF16).float(), qh.to(BF16).float()
+        k_all = torch.cat([hist[b][0], kh[None]])
+        v_all = torch.cat([hist[b][1], vh[None]])
+        ref = _last_query_attention(qh, k_all, v_all, window)
+        assert float((out2[b].cpu().float() - ref).abs().max()) < 2 ** -6, (b, s)
+
+
 @pytest.mark.parametrize("tensor_memory", [True, False])
 @pytest.mark.parametrize("nq,nkv,d,window", [(8, 2, 128, 0), (4, 2, 64, 0), (6, 2, 64, 0), (5, 1, 128, 0),
                                             (16, 1, 64, 0), (2, 2, 128, 0), (8, 2, 128, 70), (4, 2, 64, 24)])
