@@ -15,7 +15,7 @@
 // B = weights, BN up to 256 (prompt-sized products go to the two-SM kernel further down).
 // With few rows (decode, short prompts) the roles are swapped: A = weights, so that the
 // 128-row side of the MMA is filled by weight rows, and B = the activations padded to
-// 16/32/64/128/256 rows; the product is then a stream over the weights with a deep TMA ring, and k may be split
+// 16/32/64/128/256 rows; the product is then a stream over the weights through a TMA ring of five to eight stages (see TC_TRIGGER_AHEAD), and k may be split
 // over several tiles so that all SMs pull from HBM. A split writes partial sums [S, M, N] that
 // the consumer adds in rising order; S depends on the weight's shape only.
 //
