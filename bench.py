@@ -198,7 +198,8 @@ def timings_pass(eng, B, model_cfg):
         products[(H, qw)] = "o_or_down"
     names = {"lumen_add_rmsnorm": "norm", "lumen_qk_norm_rope_store": "qk_norm_rope_store",
              "lumen_rope_table": "rope_table", "lumen_silu_mul": "silu_mul", "lumen_embed": "embed",
-             "lumen_attn_decode": "attention", "lumen_attn_prefill_tc": "attention",
+             "lumen_attn_decode": "attention", "lumen_attn_decode_qkv": "attention + rotary",
+             "lumen_embed_tiled": "embed", "lumen_attn_prefill_tc": "attention",
              "lumen_attn_prefill": "attention", "lumen_attn_generic": "attention",
              "lumen_argmax": "sampling", "lumen_sample": "sampling", "lumen_gemm_tc_qkv": "qkv"}
 
