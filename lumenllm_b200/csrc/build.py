@@ -34,6 +34,7 @@ MODULES = {
     "attn_decode": (["attn_decode.cu"], ["common.cuh", "mma_utils.cuh", "qk_head.cuh", "attn_decode_noalloc.h"]),
     "attn_prefill": (["attn_prefill.cu"], ["common.cuh", "mma_utils.cuh"]),
     "attn_prefill_tc": (["attn_prefill_tc.cu"], ["common.cuh", "mma_utils.cuh"]),
+    "stream_probe": (["stream_probe.cu"], ["common.cuh", "mma_utils.cuh"]),     # a measurement (kbench stream)
 }
 
 NVCC_FLAGS = [

@@ -8,6 +8,8 @@
     python -m lumenllm_b200.kbench gemm_qkv --m 2048 --k 4096 --heads 32 --kv-heads 8
     python -m lumenllm_b200.kbench argmax --m 8 --n 151936
     python -m lumenllm_b200.kbench sample --m 8 --n 151936 [--top-k 50] [--top-p 0.9]
+    python -m lumenllm_b200.kbench stream --blocks 148 --k 4096 --stages 6 [--tiled]   (no kernel of the
+        model: blocks that only stream 16 KB stages into shared memory, csrc/stream_probe.cu)
 
 Each run cycles through `--copies` distinct operand sets (more bytes than the L2 holds, so
 that what is timed comes from HBM), times `--reps` passes with CUDA events after a warm-up and
@@ -18,7 +20,7 @@ from __future__ import annotations
 
 import argparse
 import math
-from ctypes import c_int
+from ctypes import c_int, c_void_p
 
 import torch
 
@@ -59,7 +61,7 @@ def _paged(B, length, nkv, d, dev):
 def main(argv=None):
     ap = argparse.ArgumentParser(prog="kbench")
     ap.add_argument("kernel", choices=["gemm_tc", "attn_decode", "attn_prefill",
-                                       "add_rmsnorm", "qk_rope", "gemm_qkv", "argmax", "sample"])
+                                       "add_rmsnorm", "qk_rope", "gemm_qkv", "argmax", "sample", "stream"])
     ap.add_argument("--splits", type=int, default=1, help="add_rmsnorm: partial sums to add")
     ap.add_argument("--top-k", type=int, default=0)
     ap.add_argument("--top-p", type=float, default=1.0)
@@ -82,6 +84,10 @@ def main(argv=None):
     ap.add_argument("--single-sm", action="store_true",
                     help="gemm_tc: keep prompt-sized products on the single-SM kernel")
     ap.add_argument("--bn", type=int, default=0, help="gemm_tc: fix the single-SM kernel's tile width")
+    ap.add_argument("--blocks", type=int, default=148, help="stream: blocks, one an SM")
+    ap.add_argument("--stages", type=int, default=6, help="stream: 16 KB stages of a block's ring")
+    ap.add_argument("--tiled", action="store_true",
+                    help="stream: the matrix in the tiled form of the products' weights (else row-major)")
     ap.add_argument("--seg-pages", type=int, default=0,
                     help="attn_decode: pages a block walks (default: the product's rule)")
     a = ap.parse_args(argv)
@@ -107,6 +113,20 @@ def main(argv=None):
         nbytes = a.n * a.k * 2 + a.m * a.k * 2
         flops = 2.0 * a.m * a.n * a.k
         note = f"{nbytes / us / 1e3:.0f} GB/s  {flops / us / 1e6:.1f} TFLOP/s"
+    elif a.kernel == "stream":
+        # blocks x (k / 64) stages of 16 KB: what the SMs take in when nothing is done with it
+        nkb = max(1, a.k // 64)
+        nbytes = a.blocks * nkb * 16384
+        bufs = [torch.full((nbytes,), i + 1, dtype=torch.uint8, device=dev) for i in range(a.copies)]
+        scratch = torch.zeros(2, dtype=torch.int32, device=dev)
+        f = native.fn("stream_probe", "lumen_stream_probe", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        fns = [lambda b=b: native.check(f(b.data_ptr(), a.blocks, nkb, a.stages, 1 if a.tiled else 0,
+                                          scratch.data_ptr(), native.stream_ptr()), "stream_probe") for b in bufs]
+        us = _time(fns, a.reps)
+        if int(scratch[0]) != 0:
+            raise native.KernelError("stream: a copy never arrived")
+        note = (f"{nbytes / us / 1e3:.0f} GB/s  {nbytes / a.blocks / us / 1e3:.1f} GB/s a block  "
+                f"{us * 1e3 / nkb:.0f} ns a stage  ({'tiled' if a.tiled else 'row-major'}, {a.stages} stages)")
     elif a.kernel == "attn_decode":
         sets = [_paged(a.batch, a.len, a.kv_heads, a.head_dim, dev) for _ in range(a.copies)]
         q = torch.randn(a.batch, a.heads, a.head_dim, device=dev).to(bf)
