@@ -9,6 +9,11 @@
 //         rows x 128 bytes (128-byte swizzle), its rows a whole matrix row apart.
 // mode 1: the matrix is in the tiled form of csrc/gemm_tc.cu (k block after k block, 128-byte
 //         rows in a row); a stage is a tensor copy of 128 such rows, 16 KB in one piece.
+// mode 2: tiled form as in mode 1, but the matrix has `rounds` times as many tiles as there are
+//         blocks, and a block streams all k blocks of tile b, then of tile b + G, ... as the
+//         weight-streaming product does with a tall weight (the k blocks of a tile lie a whole
+//         matrix of tiles apart).
+// mode 3: the same work on a matrix stored tile after tile (a tile's k blocks in a row).
 // One thread asks for the copies, one waits for them, reads a word and gives the stage back.
 // Every wait is bounded; a wait that runs out sets *err.
 #include <cuda.h>
@@ -31,7 +36,8 @@ __device__ __forceinline__ void sp_tma_2d(void* dst, const CUtensorMap* map, int
 #define SP_STAGE_BYTES 16384
 
 __global__ void __launch_bounds__(64, 1)
-stream_probe_kernel(const __grid_constant__ CUtensorMap tm, int nkb, int stages, int mode, int* err, unsigned* sink) {
+stream_probe_kernel(const __grid_constant__ CUtensorMap tm, int nkb, int stages, int mode, int rounds, int* err,
+                    unsigned* sink) {
     extern __shared__ __align__(1024) unsigned char sp_smem_raw[];
     unsigned char* smem = sp_smem_raw + ((1024u - (smem_u32(sp_smem_raw) & 1023u)) & 1023u);
     __shared__ uint64_t full[SP_MAX_STAGES], empty[SP_MAX_STAGES];
@@ -41,16 +47,19 @@ stream_probe_kernel(const __grid_constant__ CUtensorMap tm, int nkb, int stages,
     }
     __syncthreads();
     if (threadIdx.x == 0) {
-        for (int it = 0; it < nkb; ++it) {
+        const int tiles = gridDim.x * rounds;
+        for (int it = 0; it < nkb * rounds; ++it) {
             const int st = it % stages, ph = (it / stages) & 1;
             if (it >= stages && !mbar_wait(&empty[st], ph ^ 1)) { atomicExch(err, 1); break; }
             mbar_expect_tx(&full[st], SP_STAGE_BYTES);
-            if (mode == 0) sp_tma_2d(smem + st * SP_STAGE_BYTES, &tm, it * 64, blockIdx.x * 128, &full[st]);
-            else           sp_tma_2d(smem + st * SP_STAGE_BYTES, &tm, 0, (it * gridDim.x + blockIdx.x) * 128, &full[st]);
+            const int kb = it % nkb, tile = blockIdx.x + (it / nkb) * gridDim.x;
+            if (mode == 0)      sp_tma_2d(smem + st * SP_STAGE_BYTES, &tm, it * 64, blockIdx.x * 128, &full[st]);
+            else if (mode == 3) sp_tma_2d(smem + st * SP_STAGE_BYTES, &tm, 0, (tile * nkb + kb) * 128, &full[st]);
+            else                sp_tma_2d(smem + st * SP_STAGE_BYTES, &tm, 0, (kb * tiles + tile) * 128, &full[st]);
         }
     } else if (threadIdx.x == 32) {
         unsigned acc = 0;
-        for (int it = 0; it < nkb; ++it) {
+        for (int it = 0; it < nkb * rounds; ++it) {
             const int st = it % stages, ph = (it / stages) & 1;
             if (!mbar_wait(&full[st], ph)) { atomicExch(err, 1); break; }
             acc += *reinterpret_cast<volatile unsigned*>(smem + st * SP_STAGE_BYTES + 4 * (it & 1023));
@@ -64,9 +73,12 @@ typedef CUresult (*SpEncodeFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, vo
                                const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
                                CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
 
-// base: G * nkb * 16 KB of device memory, 1,024-byte aligned; scratch: two ints (error flag, sink).
-LUMEN_API int lumen_stream_probe(void* base, int G, int nkb, int stages, int mode, int* scratch, cudaStream_t stream) {
-    if (G < 1 || nkb < 1 || stages < 1 || stages > SP_MAX_STAGES || (mode != 0 && mode != 1) || !base || !scratch ||
+// base: G * rounds * nkb * 16 KB of device memory, 1,024-byte aligned (rounds = 1 for modes 0 and 1);
+// scratch: two ints (error flag, sink).
+LUMEN_API int lumen_stream_probe(void* base, int G, int nkb, int stages, int mode, int rounds, int* scratch,
+                                 cudaStream_t stream) {
+    if (mode < 2) rounds = 1;
+    if (G < 1 || nkb < 1 || rounds < 1 || stages < 1 || stages > SP_MAX_STAGES || mode < 0 || mode > 3 || !base || !scratch ||
         ((uintptr_t)base & 1023))
         return LUMEN_ERR_BAD_ARGUMENT;
     static SpEncodeFn fn = nullptr;
@@ -81,9 +93,9 @@ LUMEN_API int lumen_stream_probe(void* base, int G, int nkb, int stages, int mod
     CUtensorMap map;
     cuuint64_t dims[2] = {(cuuint64_t)nkb * 64, (cuuint64_t)G * 128};
     cuuint64_t strides[1] = {(cuuint64_t)nkb * 128};
-    if (mode == 1) {
+    if (mode >= 1) {
         dims[0] = 64;
-        dims[1] = (cuuint64_t)nkb * G * 128;
+        dims[1] = (cuuint64_t)nkb * G * rounds * 128;
         strides[0] = 128;
     }
     cuuint32_t box[2] = {64, 128};
@@ -99,7 +111,7 @@ LUMEN_API int lumen_stream_probe(void* base, int G, int nkb, int stages, int mod
         if (e != cudaSuccess) return (int)e;
         attr_set = smem;
     }
-    stream_probe_kernel<<<G, 64, smem, stream>>>(map, nkb, stages, mode, scratch, (unsigned*)(scratch + 1));
+    stream_probe_kernel<<<G, 64, smem, stream>>>(map, nkb, stages, mode, rounds, scratch, (unsigned*)(scratch + 1));
     LUMEN_LAUNCH_CHECK();
     return 0;
 }

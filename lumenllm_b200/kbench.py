@@ -88,6 +88,10 @@ def main(argv=None):
     ap.add_argument("--stages", type=int, default=6, help="stream: 16 KB stages of a block's ring")
     ap.add_argument("--tiled", action="store_true",
                     help="stream: the matrix in the tiled form of the products' weights (else row-major)")
+    ap.add_argument("--rounds", type=int, default=0,
+                    help="stream: tiles a block streams one after the other, all k blocks of each (tiled form)")
+    ap.add_argument("--tile-major", action="store_true",
+                    help="stream, with --rounds: the matrix stored tile after tile instead of k block after k block")
     ap.add_argument("--seg-pages", type=int, default=0,
                     help="attn_decode: pages a block walks (default: the product's rule)")
     a = ap.parse_args(argv)
@@ -116,17 +120,19 @@ def main(argv=None):
     elif a.kernel == "stream":
         # blocks x (k / 64) stages of 16 KB: what the SMs take in when nothing is done with it
         nkb = max(1, a.k // 64)
-        nbytes = a.blocks * nkb * 16384
+        rounds = max(1, a.rounds)
+        mode = (3 if a.tile_major else 2) if a.rounds else (1 if a.tiled else 0)
+        nbytes = a.blocks * rounds * nkb * 16384
         bufs = [torch.full((nbytes,), i + 1, dtype=torch.uint8, device=dev) for i in range(a.copies)]
         scratch = torch.zeros(2, dtype=torch.int32, device=dev)
-        f = native.fn("stream_probe", "lumen_stream_probe", [c_void_p, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
-        fns = [lambda b=b: native.check(f(b.data_ptr(), a.blocks, nkb, a.stages, 1 if a.tiled else 0,
+        f = native.fn("stream_probe", "lumen_stream_probe", [c_void_p, c_int, c_int, c_int, c_int, c_int, c_void_p, c_void_p])
+        fns = [lambda b=b: native.check(f(b.data_ptr(), a.blocks, nkb, a.stages, mode, rounds,
                                           scratch.data_ptr(), native.stream_ptr()), "stream_probe") for b in bufs]
         us = _time(fns, a.reps)
         if int(scratch[0]) != 0:
             raise native.KernelError("stream: a copy never arrived")
         note = (f"{nbytes / us / 1e3:.0f} GB/s  {nbytes / a.blocks / us / 1e3:.1f} GB/s a block  "
-                f"{us * 1e3 / nkb:.0f} ns a stage  ({'tiled' if a.tiled else 'row-major'}, {a.stages} stages)")
+                f"{us * 1e3 / (nkb * rounds):.0f} ns a stage  ({['row-major', 'tiled', 'tiled, tile after tile of a tall matrix', 'tile-major'][mode]}, {a.stages} stages)")
     elif a.kernel == "attn_decode":
         sets = [_paged(a.batch, a.len, a.kv_heads, a.head_dim, dev) for _ in range(a.copies)]
         q = torch.randn(a.batch, a.heads, a.head_dim, device=dev).to(bf)
