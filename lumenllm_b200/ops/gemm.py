@@ -52,13 +52,18 @@ def gemm_bf16(x: torch.Tensor, w: torch.Tensor, split_ok: bool = False, add_to=N
     return part if split_ok else part.sum(dim=0)
 
 
-def gemm_gate_up_silu(x: torch.Tensor, w_interleaved: torch.Tensor):
+def gemm_gate_up_silu(x: torch.Tensor, w_interleaved):
     """silu(gate) * up in bfloat16 [M, I] from x [M, K] and a weight [2I, K] whose rows
-    alternate gate_i, up_i, in ONE kernel when there are many rows; else None. Up to 128
-    rows the product streams the weights with k split, which the epilogue cannot have, and
-    the split product with the activation kernel behind it is the faster pair (at 100 rows
-    of the 8B shape 41 + 6 us against 56 us)."""
-    if x.shape[0] > 128 and takes_tc(x, w_interleaved):
+    alternate gate_i, up_i, in ONE kernel where that is the faster way; else None, and the
+    caller takes the float32 product with the activation kernel behind it. One kernel: from 512
+    rows on, and for rows that fill the two-SM kernel's 256-row tiles. Below: up to 128 rows
+    the product streams the weights with k split, which the epilogue cannot have (at 100 rows of
+    the 8B shape 41 + 6 us against 56 us); from 129 to 511 rows the two-SM kernel works on tiles
+    that are part empty, and the split product is the faster again (first token of a prompt of
+    160 / 192 / 288 / 384 / 480 tokens at the 8B shape: 4.9 / 5.1 / 7.0 / 7.3 / 8.0 ms against
+    5.6 / 5.7 / 7.6 / 7.7 / 8.4; of 256 tokens 5.3 in one kernel against 5.5)."""
+    rows = x.shape[0]
+    if (rows >= 512 or (rows > 128 and rows % 256 == 0)) and takes_tc(x, w_interleaved):
         return K.gemm_tc(x if x.is_contiguous() else x.contiguous(), w_interleaved,
                          silu_interleaved=True)
     return None
